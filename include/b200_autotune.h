@@ -1,0 +1,140 @@
+/*
+ * b200_autotune.h -- C ABI of libb200_autotune.so
+ *
+ * The shared library holds hand-written sm_100a kernels for the one hot path of
+ * awslabs/nki-autotune: C = lhsT^T . rhs and the fused RMSNorm + matmul, plus the
+ * per-candidate timing harness the autotune loop calls.  Every entry point is plain C:
+ * device pointers travel as void*, the stream as void* (a cudaStream_t), sizes as long.
+ * Every function returns a b200_status (0 = OK) and never throws or aborts; the text
+ * of the last error on the calling thread is available from b200_last_error().
+ *
+ * Reference interfaces each entry point stands in for are cited as
+ * <file within awslabs/nki-autotune>:<line>.
+ */
+#ifndef B200_AUTOTUNE_H
+#define B200_AUTOTUNE_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+/* Status codes.  Mirrors the reference's failure classes: a candidate either runs,
+ * is rejected for on-chip capacity ("Out of memory in sbuf/psum" upstream,
+ * autotune/src/autotune/runner/output.py:236-239) or fails with a message. */
+typedef enum b200_status {
+  B200_OK = 0,
+  B200_ERR_BAD_ARG = 1,       /* NULL pointer, unknown family, misaligned pointer          */
+  B200_ERR_BAD_SHAPE = 2,     /* shape/leading dimension the kernels cannot address        */
+  B200_ERR_UNSUPPORTED = 3,   /* meta-parameter outside the implemented grid               */
+  B200_ERR_SMEM_OOM = 4,      /* pipeline does not fit the 227 KB shared-memory budget      */
+  B200_ERR_TMEM_OOM = 5,      /* accumulators do not fit the 512 tensor-memory columns      */
+  B200_ERR_CUDA = 6,          /* a CUDA runtime/driver call failed                          */
+  B200_ERR_DEVICE_WAIT = 7,   /* a bounded device-side wait expired; see dev_status[]       */
+  B200_ERR_WORKSPACE = 8      /* workspace missing or too small                             */
+} b200_status;
+
+/* Meta-parameters of one autotune candidate.  These are what the sweep enumerates in
+ * place of the reference's schedule transforms (tensorize Split factors, multi-buffer
+ * counts, SoftwarePipeline stages, Reorder; nkigym/src/nkigym/transforms/*.py) and of
+ * KernelJob.lnc (autotune/src/autotune/runner/types.py:50). */
+typedef struct b200_cfg {
+  int tile_m;     /* output-tile rows per CTA group: 128 or 256                            */
+  int tile_n;     /* output-tile columns: 32..256, multiple of 32 (16 for the skinny path) */
+  int tile_k;     /* K extent of one pipeline stage: 64 or 128                             */
+  int stages;     /* depth of the TMA -> shared-memory ring, 2..12                          */
+  int cluster_m;  /* 1, or 2 = a CTA pair along M (tile_m 256: one 2-SM UMMA)               */
+  int cluster_n;  /* 1 (reserved)                                                          */
+  int swizzle;    /* tile rasterisation group width along M (1,2,4,8,16); 0 = default      */
+  int split_k;    /* skinny rmsnorm path only: K slices per output tile; 0 = automatic      */
+  int reserved[8];
+} b200_cfg;
+
+/* Number of ints in a dev_status block (device memory, caller-owned, zeroed by caller).
+ * [0] status code (0 or B200_ERR_DEVICE_WAIT)  [1] role that gave up  [2] barrier id
+ * [3] tile index  [4] k-block index  [5] blockIdx.x  -- first failure wins. */
+#define B200_DEV_STATUS_INTS 8
+
+const char* b200_last_error(void);
+int b200_abi_version(void);
+
+/* Number of CUDA devices visible to the process.
+ * Stands in for detect_neuron_cores(), autotune/src/autotune/runner/detect.py:7-20. */
+int b200_device_count(int* count);
+
+/* Candidate validation without touching the GPU: computes the shared-memory bytes and
+ * tensor-memory columns the candidate needs and returns B200_ERR_SMEM_OOM /
+ * B200_ERR_TMEM_OOM / B200_ERR_UNSUPPORTED / B200_ERR_BAD_SHAPE when it cannot run.
+ * family is "matmul_lhsT_rhs" or "rmsnorm_matmul".
+ * Stands in for the compile step, compile_one(), autotune/src/autotune/runner/compile.py:197-244:
+ * an over-subscribed candidate is a reported failure, never silently dropped. */
+int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
+                   long* smem_bytes, int* tmem_cols);
+
+/* Bytes of device scratch the candidate needs (0 for most). */
+size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K);
+
+/* C[M,N] (bf16, row stride ld_out) = lhsT[K,M]^T . rhs[K,N], bf16 operands, fp32
+ * accumulation in tensor memory over the whole of K, bf16 result.
+ * lhsT has M contiguous (row stride ld_lhsT elements), rhs has N contiguous.
+ * Replaces matmul_lhsT_rhs_nkigym, kernel_library/matmul/lhsT_rhs/kernel_hand_90.92mfu.py:101-131.
+ * Asynchronous on `stream`; dev_status may be NULL. */
+int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out,
+                         long M, long N, long K, long ld_lhsT, long ld_rhs, long ld_out,
+                         const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
+                         int* dev_status, void* stream);
+
+/* Same contraction in fp32 on the CUDA cores (no tensor cores, no tf32): the 1e-5
+ * configuration and the on-device cross-check for the tensor-core candidates.
+ * Follows NKIMatmul._run, nkigym/src/nkigym/ops/matmul.py:43-45
+ * (stationary.astype(f32).T @ moving.astype(f32)). */
+int b200_matmul_lhsT_rhs_f32(const void* lhsT, const void* rhs, void* out,
+                             long M, long N, long K, long ld_lhsT, long ld_rhs, long ld_out,
+                             void* stream);
+
+/* out[M,N] (bf16) = (x / sqrt(mean_k x^2 + eps) * gamma) . w with x[M,K] (K contiguous),
+ * gamma[K] (bf16, may be NULL = all ones), w[K,N] (N contiguous); row statistics and
+ * accumulation in fp32.
+ * Replaces rmsnorm_matmul_online, kernel_library/rmsnorm_matmul/kernel_hand_online.py:198-353
+ * (gamma is an extension; gamma == NULL reproduces that kernel's maths). */
+int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out,
+                        long M, long N, long K, float eps,
+                        const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
+                        int* dev_status, void* stream);
+
+/* fp32 CUDA-core evaluation of the same fused expression on bf16 inputs (fp32 output),
+ * used as the on-device cross-check of b200_rmsnorm_matmul. */
+int b200_rmsnorm_matmul_f32(const void* x, const void* gamma, const void* w, void* out_f32,
+                            long M, long N, long K, float eps, void* stream);
+
+/* Times one candidate: `warmup` untimed launches, then `iters` launches each bracketed
+ * by CUDA events on `stream`; ms_each[iters] receives the per-launch milliseconds.
+ * Between launches a scratch buffer of flush_bytes (may be 0/NULL) is overwritten so
+ * that operands are not L2-resident from the previous launch.  The launch itself is
+ * the same code path as b200_matmul_lhsT_rhs / b200_rmsnorm_matmul.
+ * Stands in for benchmark_one() + extract_perf_metrics,
+ * autotune/src/autotune/runner/benchmark.py:116-153 and :58-87. */
+typedef struct b200_problem {
+  const char* family;          /* "matmul_lhsT_rhs" | "rmsnorm_matmul"                      */
+  const void* a;               /* lhsT[K,M] or x[M,K]                                      */
+  const void* b;               /* rhs[K,N]  or w[K,N]                                      */
+  const void* gamma;           /* rmsnorm only, may be NULL                                */
+  void* out;
+  long M, N, K;
+  long ld_a, ld_b, ld_out;     /* 0 = dense                                                */
+  float eps;
+  int reserved[7];
+} b200_problem;
+
+int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg,
+                     void* workspace, size_t workspace_bytes, int* dev_status,
+                     void* flush_buf, size_t flush_bytes,
+                     int warmup, int iters, float* ms_each, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_AUTOTUNE_H */

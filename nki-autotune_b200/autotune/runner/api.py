@@ -1,0 +1,76 @@
+"""Public entry point of the profiling path.
+
+``profile()`` keeps the signature, return type and cache layout of the reference
+(``autotune/src/autotune/runner/api.py:24-75``): write the candidate sources, run the
+validate-and-time pipeline, write logs and ``results.json``, return a ``ProfileOutput``.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import time
+
+from autotune.runner.driver import run_pipeline
+from autotune.runner.output import ProfileOutput, write_compiler_logs, write_kernel_sources, write_results_json
+from autotune.runner.types import KernelJob
+
+logger = logging.getLogger(__name__)
+
+SUPPORTED_TARGETS = ("b200", "sm_100a", "sm100a", "blackwell")
+
+
+def profile(
+    kernels: dict[str, KernelJob],
+    cache_dir: str,
+    seed: int,
+    neuron_platform_target: str,
+    collect_detailed_profile: bool,
+    n_gpus: int | None = None,
+    warmup: int = 3,
+    iters: int = 10,
+) -> ProfileOutput:
+    """Validate and time a set of candidates on the GPUs of this box.
+
+    Args:
+        kernels: Candidate file name -> ``KernelJob``.
+        cache_dir: Directory for sources, logs, per-candidate JSON and ``results.json``; the
+            empty string skips all disk output.
+        seed: Seed of the input tensors (one ``numpy.random.default_rng(seed)`` per batch).
+        neuron_platform_target: Kept from the reference signature.  ``"b200"`` / ``"sm_100a"``
+            name this backend; the reference's ``"trn2"`` is accepted and ignored so existing
+            drivers run unchanged.
+        collect_detailed_profile: Attach the per-launch timing list as ``profile.json``.
+        n_gpus: Optional cap on the number of GPUs the sweep is sharded over (extension).
+        warmup, iters: Untimed and timed launches per candidate (extension).
+
+    Returns:
+        ``ProfileOutput`` with every candidate present, as a success or as a failure row.
+    """
+    os.environ["B200_AUTOTUNE_TARGET"] = neuron_platform_target
+    if neuron_platform_target.lower() not in SUPPORTED_TARGETS:
+        logger.info("platform target %r is not a B200 name; running on the local GPUs anyway", neuron_platform_target)
+    keep_logs = bool(cache_dir)
+    if cache_dir:
+        os.makedirs(cache_dir, exist_ok=True)
+        write_kernel_sources(cache_dir, kernels)
+
+    start = time.monotonic()
+    results, compiler_logs = run_pipeline(
+        kernels,
+        seed=seed,
+        collect_compiler_logs=keep_logs,
+        collect_detailed_profile=collect_detailed_profile,
+        n_gpus=n_gpus,
+        warmup=warmup,
+        iters=iters,
+    )
+    elapsed_s = time.monotonic() - start
+    logger.info("Profile complete: %d results in %.1fs", len(results), elapsed_s)
+
+    if cache_dir:
+        write_compiler_logs(cache_dir, compiler_logs)
+        write_results_json(cache_dir, len(kernels), results, elapsed_s)
+        logger.info("Cache saved to %s", cache_dir)
+
+    return ProfileOutput(results=results, compiler_logs=compiler_logs, elapsed_s=elapsed_s, cache_dir=cache_dir)

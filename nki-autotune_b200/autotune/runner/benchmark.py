@@ -1,0 +1,202 @@
+"""Timing and checking of one candidate on the GPU, and seeded input generation.
+
+Upstream ``benchmark_one`` (``autotune/src/autotune/runner/benchmark.py:116-153``) runs the
+compiled kernel once under the Neuron profiler and returns the profiler's summary dict.
+Here the candidate is launched through the C ABI, timed with CUDA events inside the library
+(warm-up + repeated launches, median), and its output is compared with a reference result
+computed once per batch; the summary dict keeps the keys ``output.py`` consumes
+(``total_time`` in seconds; ``mfu_estimated_percent``, ``mbu_estimated_percent`` and
+``mfu_max_achievable_estimated_percent`` as fractions).
+"""
+
+from __future__ import annotations
+
+import statistics
+from typing import Any
+
+import numpy as np
+
+from autotune.peaks import load_peaks
+from autotune.runner.candidate import Candidate
+from autotune.runner.types import CompileResult, OutputSpec, ProfileResult, capture_error, resolve_dtype
+
+TOL_BF16 = 1e-2   # max |a-e| / (|e| + rms(e)) for bf16 inputs, fp32 accumulation, bf16 output
+TOL_FP32 = 1e-5   # same metric for the fp32 configuration
+
+
+def generate_tensors(tensor_specs: dict[str, dict], seed: int) -> dict[str, np.ndarray]:
+    """Seeded inputs: one ``default_rng(seed)``, tensors drawn in dict order.
+
+    Same contract as the reference (benchmark.py:156-169: ``standard_normal(shape).astype(dtype)``),
+    extended with an optional per-tensor ``"dist"``: ``{"kind": "normal", "scale": s}`` multiplies
+    the normal draw by ``s``; ``{"kind": "uniform", "low": a, "high": b}`` draws ``uniform(a, b)``.
+    """
+    rng = np.random.default_rng(seed)
+    tensors: dict[str, np.ndarray] = {}
+    for name, spec in tensor_specs.items():
+        shape = tuple(spec["shape"])
+        dtype = resolve_dtype(spec["dtype"])
+        dist = spec.get("dist") or {"kind": "normal", "scale": 1.0}
+        if dist["kind"] == "normal":
+            values = rng.standard_normal(shape)
+            scale = float(dist.get("scale", 1.0))
+            if scale != 1.0:
+                values *= scale
+        elif dist["kind"] == "uniform":
+            values = rng.uniform(float(dist["low"]), float(dist["high"]), shape)
+        else:
+            raise ValueError(f"unknown distribution {dist!r} for tensor {name!r}")
+        tensors[name] = values.astype(dtype)
+    return tensors
+
+
+def algorithmic_work(family: str, M: int, N: int, K: int, elem_bytes: int) -> tuple[float, float]:
+    """(FLOPs, compulsory bytes): every operand read once, the output written once."""
+    flops = 2.0 * M * N * K
+    if family == "matmul_lhsT_rhs":
+        nbytes = (K * M + K * N + M * N) * elem_bytes
+    else:
+        nbytes = (M * K + K * N + M * N + K) * elem_bytes
+    return flops, float(nbytes)
+
+
+def max_rel_err(actual, expected) -> float:
+    """max |a-e| / (|e| + rms(e)) on torch tensors (fp32 arithmetic)."""
+    import torch
+
+    e = expected.float()
+    a = actual.float()
+    floor = torch.sqrt(torch.mean(e * e)).clamp_min(1e-30)
+    return float(torch.max(torch.abs(a - e) / (torch.abs(e) + floor)))
+
+
+class DeviceBatch:
+    """Device-resident inputs, reference output and scratch shared by a batch of candidates."""
+
+    def __init__(self, family: str, kwargs: dict[str, np.ndarray], out: OutputSpec, scalars: dict, device: str = "cuda"):
+        import torch
+
+        from autotune import kernels
+
+        self.family = family
+        self.out_spec = out
+        self.device = device
+        self.scalars = dict(scalars)
+        names = list(kwargs)
+        self.host = kwargs
+        self.tensors = {n: kernels.to_device(np.asarray(v), device) for n, v in kwargs.items()}
+        self.a = self.tensors[names[0]]
+        self.b = self.tensors[names[-1]]
+        self.gamma = self.tensors[names[1]] if (family == "rmsnorm_matmul" and len(names) == 3) else None
+        self.is_fp32 = self.a.dtype == torch.float32
+        if family == "matmul_lhsT_rhs":
+            self.K, self.M = self.a.shape
+        else:
+            self.M, self.K = self.a.shape
+        self.N = self.b.shape[1]
+        self.out = torch.empty((self.M, self.N), dtype=self.a.dtype, device=device)
+        self.status = kernels.new_status(device)
+        # larger than the 126 MB L2, overwritten between timed launches
+        self.flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=device)
+        self.reference = self._reference()
+
+    def _reference(self):
+        """fp32 CUDA-core result on the same (bf16-rounded) inputs."""
+        import torch
+
+        from autotune import kernels
+
+        if self.family == "matmul_lhsT_rhs":
+            ref = kernels.matmul_lhsT_rhs(self.a.float(), self.b.float())
+        else:
+            ref = kernels.rmsnorm_matmul_f32(self.a, self.gamma, self.b, float(self.scalars.get("eps", 1e-6)))
+        torch.cuda.synchronize()
+        return ref
+
+
+def benchmark_one(
+    batch: DeviceBatch,
+    cr: CompileResult,
+    candidate: Candidate,
+    warmup: int = 3,
+    iters: int = 10,
+    collect_detailed_profile: bool = False,
+) -> ProfileResult:
+    """Time one validated candidate and check its output; never raises (reference: benchmark.py:116-153)."""
+    import torch
+
+    from autotune import kernels
+
+    out = batch.out_spec
+    hardware_output = f"{list(out.shape)} {out.dtype}"
+    summary: dict[str, Any] | None = None
+    detailed: dict[str, Any] | None = None
+    try:
+        batch.out.zero_()
+        batch.status.zero_()
+        eps = float(candidate.scalars.get("eps", batch.scalars.get("eps", 1e-6)))
+        if batch.is_fp32:
+            if batch.family != "matmul_lhsT_rhs":
+                raise ValueError("fp32 inputs are implemented for matmul_lhsT_rhs only")
+            ms = _time_fp32(batch, warmup, iters)
+        else:
+            ms = kernels.time_kernel(
+                batch.family, batch.a, batch.b, batch.out, candidate.config, gamma=batch.gamma, eps=eps,
+                warmup=warmup, iters=iters, flush=batch.flush, status=batch.status,
+            )
+        torch.cuda.synchronize()
+        err = max_rel_err(batch.out, batch.reference)
+        tol = TOL_FP32 if batch.is_fp32 else TOL_BF16
+        if not (err <= tol):
+            raise AssertionError(f"parity check failed: max-abs-rel error {err:.3e} > {tol:.0e}")
+        peaks = load_peaks()
+        t = statistics.median(ms) * 1e-3
+        flops, nbytes = algorithmic_work(batch.family, batch.M, batch.N, batch.K, batch.a.element_size())
+        peak_flops = peaks["bf16_tflops"] * 1e12
+        peak_bw = peaks["hbm_gbs"] * 1e9
+        summary = {
+            "total_time": t,
+            "mfu_estimated_percent": flops / (t * peak_flops) if not batch.is_fp32 else 0.0,
+            "mbu_estimated_percent": nbytes / (t * peak_bw),
+            "mfu_max_achievable_estimated_percent": min(1.0, (flops / nbytes) * peak_bw / peak_flops),
+            "tflops": flops / t / 1e12,
+            "gbytes_per_s": nbytes / t / 1e9,
+            "time_ms_each": [float(x) for x in ms],
+            "time_ms_min": float(min(ms)),
+            "max_abs_rel_err": err,
+            "tolerance": tol,
+            "config": dict(candidate.config),
+            "peaks": peaks,
+            "device": torch.cuda.get_device_name(torch.cuda.current_device()),
+            "device_index": torch.cuda.current_device(),
+        }
+        if collect_detailed_profile:
+            detailed = {"launches_ms": [float(x) for x in ms], "warmup": warmup, "iters": iters}
+    except Exception as exc:  # noqa: BLE001 - every failure becomes a row
+        hardware_output = capture_error(exc)
+        summary = None
+    return ProfileResult(
+        kernel_name=cr.kernel_name,
+        hardware_output=hardware_output,
+        profiler_summary=summary,
+        profile_detailed=detailed,
+    )
+
+
+def _time_fp32(batch: DeviceBatch, warmup: int, iters: int) -> list[float]:
+    """CUDA-event timing of the fp32 CUDA-core kernel (torch events on the current stream)."""
+    import torch
+
+    from autotune import kernels
+
+    for _ in range(warmup):
+        kernels.matmul_lhsT_rhs(batch.a, batch.b, out=batch.out)
+    ms = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        kernels.matmul_lhsT_rhs(batch.a, batch.b, out=batch.out)
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    return ms

@@ -1,0 +1,314 @@
+"""Sweep orchestration: validate every candidate, shard the accepted ones over the GPUs of
+the box, time each on its GPU, gather the results on the host.
+
+Mirrors ``run_pipeline`` (``autotune/src/autotune/runner/driver.py:126-165``): per-candidate
+failures never raise, batch misuse does.  Differences that follow from the hardware: the
+"compile" stage is a budget check (no compiler runs), and the serial benchmark loop on one
+NeuronCore becomes one worker process per GPU.  Candidate ``i`` of the accepted list goes to
+GPU ``i mod G``; workers are independent, there is no collective and no peer access -- results
+travel back over pipes.  A worker that dies or overruns its deadline costs only the candidate
+it was on: that candidate becomes a failure row and a fresh worker takes over the rest.
+"""
+
+from __future__ import annotations
+
+import logging
+import multiprocessing as mp
+import os
+import shutil
+import tempfile
+import time
+from pathlib import Path
+from typing import Any, Callable
+
+from autotune.runner.candidate import parse_source
+from autotune.runner.compile import compile_one
+from autotune.runner.types import (
+    CompileResult,
+    KernelJob,
+    OutputSpec,
+    ProfileResult,
+    capture_error,
+    compile_failure_result,
+    make_failure,
+    resolve_dtype,
+)
+
+logger = logging.getLogger(__name__)
+
+_OUTPUT_TENSOR_NAME = "hbm_tensor_0"
+DEFAULT_DEADLINE_S = 300.0
+
+
+def _tensor_specs(job: KernelJob) -> dict[str, dict]:
+    specs = {}
+    for name, spec in job.input_specs.items():
+        shape, dtype = spec[0], spec[1]
+        entry: dict[str, Any] = {"shape": list(shape), "dtype": dtype}
+        if len(spec) > 2 and spec[2]:
+            entry["dist"] = dict(spec[2])
+        specs[name] = entry
+    return specs
+
+
+def _prepare_kernel(kname: str, job: KernelJob, nki_dir: Path) -> dict[str, Any]:
+    """Write the descriptor to disk and collect what a worker needs (reference: driver.py:35-52)."""
+    filename = kname if kname.endswith(".py") else f"{kname}.py"
+    path = nki_dir / filename
+    path.write_text(job.source)
+    return {
+        "kernel_name": kname,
+        "nki_path": str(path),
+        "func_name": job.func_name,
+        "output_shape": tuple(job.output_shape),
+        "tensor_specs": _tensor_specs(job),
+        "input_dtype_name": next(iter(job.input_specs.values()))[1],
+        "source": job.source,
+    }
+
+
+def shard_round_robin(items: list, n_workers: int) -> list[list]:
+    """Item ``i`` goes to worker ``i mod n_workers`` (deterministic)."""
+    shards: list[list] = [[] for _ in range(max(1, n_workers))]
+    for i, item in enumerate(items):
+        shards[i % len(shards)].append(item)
+    return shards
+
+
+# ----------------------------------------------------------------------------- GPU worker body
+def gpu_shard_worker(items: list[dict], opts: dict, emit: Callable[[ProfileResult], None]) -> None:
+    """Time every candidate of one shard on the current process's GPU 0.
+
+    Inputs are regenerated from the seed in this process (same seed -> same tensors on every
+    GPU), grouped so that candidates that share input specs share one device copy.
+    """
+    from autotune.runner.benchmark import DeviceBatch, benchmark_one, generate_tensors
+
+    batches: dict[str, Any] = {}
+    for kd in items:
+        cr = CompileResult(kd["kernel_name"], kd["nki_path"], "", "")
+        try:
+            cand = parse_source(kd["source"])
+            key = repr((kd["func_name"], kd["tensor_specs"], kd["output_shape"], sorted(cand.scalars.items())))
+            if key not in batches:
+                batches.clear()  # one batch resident at a time bounds device memory
+                kwargs = generate_tensors(kd["tensor_specs"], opts["seed"])
+                out = OutputSpec(_OUTPUT_TENSOR_NAME, kd["output_shape"], resolve_dtype(kd["input_dtype_name"]))
+                batches[key] = DeviceBatch(kd["func_name"], kwargs, out, cand.scalars)
+            result = benchmark_one(
+                batches[key], cr, cand, warmup=opts["warmup"], iters=opts["iters"],
+                collect_detailed_profile=opts["detailed"],
+            )
+        except Exception as exc:  # noqa: BLE001
+            result = make_failure(kd["kernel_name"], capture_error(exc))
+        emit(result)
+
+
+# ----------------------------------------------------------------------------- process pool
+def _child_main(worker_fn, items, opts, device_env, conn) -> None:
+    """Entry point of a worker process: pin the GPU before any CUDA library is imported."""
+    if device_env is not None:
+        os.environ["CUDA_VISIBLE_DEVICES"] = device_env
+    try:
+        worker_fn(items, opts, lambda r: conn.send(("result", tuple(r))))
+        conn.send(("done", None))
+    except BaseException as exc:  # noqa: BLE001
+        try:
+            conn.send(("crash", capture_error(exc)))
+        except Exception:  # noqa: BLE001
+            pass
+    finally:
+        conn.close()
+
+
+def run_sharded(
+    shards: list[list[dict]],
+    worker_fn: Callable,
+    opts: dict,
+    device_envs: list[str | None],
+    deadline_s: float = DEFAULT_DEADLINE_S,
+    startup_s: float = 600.0,
+) -> list[ProfileResult]:
+    """Run one worker process per shard and gather ``ProfileResult`` rows on the host.
+
+    Each item must carry ``"kernel_name"``.  ``worker_fn(items, opts, emit)`` must call
+    ``emit`` once per item, in order.  The first result of a worker may take ``startup_s``
+    (process start, CUDA context, input generation); every later one ``deadline_s``.
+    """
+    ctx = mp.get_context("spawn")
+    results: list[ProfileResult] = []
+
+    class _Slot:
+        def __init__(self, idx: int, items: list[dict]):
+            self.idx = idx
+            self.pending = list(items)
+            self.proc = None
+            self.conn = None
+            self.deadline = 0.0
+            self.fresh = True
+
+        def start(self) -> None:
+            parent, child = ctx.Pipe(duplex=False)
+            self.proc = ctx.Process(
+                target=_child_main, args=(worker_fn, list(self.pending), opts, device_envs[self.idx], child),
+                daemon=True,
+            )
+            self.proc.start()
+            child.close()
+            self.conn = parent
+            self.fresh = True
+            self.deadline = time.monotonic() + startup_s
+
+        def stop(self) -> None:
+            if self.proc is not None:
+                if self.proc.is_alive():
+                    self.proc.terminate()  # exactly the PID this pool started
+                self.proc.join(timeout=10)
+                if self.proc.is_alive():
+                    self.proc.kill()
+                    self.proc.join(timeout=10)
+            if self.conn is not None:
+                self.conn.close()
+            self.proc = None
+            self.conn = None
+
+    slots = [_Slot(i, items) for i, items in enumerate(shards) if items]
+    for s in slots:
+        s.start()
+
+    def _fail_current(slot: _Slot, why: str) -> None:
+        item = slot.pending.pop(0)
+        results.append(make_failure(item["kernel_name"], why))
+        slot.stop()
+        if slot.pending:
+            slot.start()
+
+    active = [s for s in slots if s.pending]
+    while active:
+        progressed = False
+        for slot in list(active):
+            try:
+                has_msg = slot.conn.poll(0.05)
+            except (EOFError, OSError):
+                has_msg = False
+            if has_msg:
+                try:
+                    kind, payload = slot.conn.recv()
+                except (EOFError, OSError):
+                    kind, payload = "eof", None
+                progressed = True
+                if kind == "result":
+                    res = ProfileResult(*payload)
+                    if slot.pending and slot.pending[0]["kernel_name"] == res.kernel_name:
+                        slot.pending.pop(0)
+                    else:
+                        slot.pending = [it for it in slot.pending if it["kernel_name"] != res.kernel_name]
+                    results.append(res)
+                    slot.fresh = False
+                    slot.deadline = time.monotonic() + deadline_s
+                elif kind == "done":
+                    for item in slot.pending:
+                        results.append(make_failure(item["kernel_name"], "worker finished without a result"))
+                    slot.pending = []
+                    slot.stop()
+                elif kind == "crash":
+                    _fail_current(slot, f"worker crashed:\n{payload}")
+                else:
+                    _fail_current(slot, "worker exited without reporting (pipe closed)")
+            elif slot.proc is not None and not slot.proc.is_alive():
+                # drain anything it managed to send before dying
+                if not slot.conn.poll(0):
+                    _fail_current(slot, f"worker process died (exit code {slot.proc.exitcode})")
+                    progressed = True
+            elif time.monotonic() > slot.deadline:
+                limit = startup_s if slot.fresh else deadline_s
+                _fail_current(slot, f"worker exceeded its {limit:.0f} s deadline and was stopped")
+                progressed = True
+            if not slot.pending:
+                slot.stop()
+                active.remove(slot)
+        if not progressed:
+            time.sleep(0.01)
+    return results
+
+
+# ----------------------------------------------------------------------------- pipeline
+def _visible_devices(n_detected: int) -> list[str]:
+    env = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if env:
+        return [d.strip() for d in env.split(",") if d.strip()][:n_detected]
+    return [str(i) for i in range(n_detected)]
+
+
+def run_pipeline(
+    kernels: dict[str, KernelJob],
+    seed: int,
+    collect_compiler_logs: bool,
+    collect_detailed_profile: bool,
+    n_gpus: int | None = None,
+    warmup: int = 3,
+    iters: int = 10,
+    deadline_s: float = DEFAULT_DEADLINE_S,
+) -> tuple[list[ProfileResult], dict[str, str]]:
+    """Validate + time every candidate; returns ``(results, compiler_logs)``.
+
+    ``n_gpus`` (or the environment variable ``B200_AUTOTUNE_GPUS``) caps the number of GPUs
+    used; the default is every visible GPU.  With one GPU the shard runs in this process.
+    """
+    from autotune.runner.detect import detect_gpus
+
+    lncs = {int(job.lnc) for job in kernels.values()}
+    if len(lncs) > 1:
+        raise RuntimeError(f"Batch mixes lnc values {lncs}; submit one lnc per profile() call")
+    if not kernels:
+        return [], {}
+
+    first_job = next(iter(kernels.values()))
+    work_dir = Path(tempfile.mkdtemp(prefix=f"autotune-{first_job.func_name}-"))
+    nki_dir = work_dir / "nki"
+    log_dir = work_dir / "log"
+    nki_dir.mkdir()
+    log_dir.mkdir()
+    try:
+        detected = detect_gpus()
+        want = n_gpus if n_gpus is not None else int(os.environ.get("B200_AUTOTUNE_GPUS", "0") or 0)
+        n_use = min(detected, want) if want > 0 else detected
+        logger.info("Driver ready: %d kernels, %d CPU, %d/%d GPU", len(kernels), os.cpu_count() or 1, n_use, detected)
+
+        prepared = {k: _prepare_kernel(k, job, nki_dir) for k, job in kernels.items()}
+
+        compile_results: list[CompileResult] = []
+        compile_errors: list[ProfileResult] = []
+        accepted: list[dict] = []
+        for kname, kd in prepared.items():
+            shapes = {n: tuple(s["shape"]) for n, s in kd["tensor_specs"].items()}
+            stem_dir = log_dir / Path(kname).stem
+            stem_dir.mkdir(parents=True, exist_ok=True)
+            cr = compile_one(
+                kname, kd["nki_path"], kd["func_name"], shapes, kd["input_dtype_name"], kd["output_shape"],
+                log_path=str(stem_dir / "log-neuron-cc.txt"),
+            )
+            compile_results.append(cr)
+            if cr.error:
+                compile_errors.append(compile_failure_result(cr))
+            else:
+                accepted.append(kd)
+
+        opts = {"seed": seed, "warmup": warmup, "iters": iters, "detailed": collect_detailed_profile}
+        hw_results: list[ProfileResult] = []
+        if accepted:
+            if n_use <= 1:
+                gpu_shard_worker(accepted, opts, hw_results.append)
+            else:
+                shards = shard_round_robin(accepted, n_use)
+                hw_results = run_sharded(shards, gpu_shard_worker, opts, _visible_devices(n_use), deadline_s)
+
+        logs: dict[str, str] = {}
+        if collect_compiler_logs:
+            for cr in compile_results:
+                p = log_dir / Path(cr.kernel_name).stem / "log-neuron-cc.txt"
+                if p.exists():
+                    logs[cr.kernel_name] = p.read_text()
+        return compile_errors + hw_results, logs
+    finally:
+        shutil.rmtree(work_dir, ignore_errors=True)

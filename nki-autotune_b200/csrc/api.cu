@@ -1,0 +1,444 @@
+// Host side of libb200_autotune.so: candidate validation, tensor-map construction, launches of
+// the tcgen05 kernels, and the CUDA-event timing harness.  Plain C ABI (include/b200_autotune.h).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <vector>
+
+#include "gemm_tcgen05.cuh"
+#include "host_api.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------- errors
+static thread_local char g_last_error[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return B200_OK;
+  return set_error(B200_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+// ---------------------------------------------------------------------------- plan
+constexpr long SMEM_BUDGET = 232448;  // 227 KB: largest opt-in dynamic shared memory per CTA
+
+enum Family { FAM_LHST = 0, FAM_RMSNORM = 1, FAM_UNKNOWN = -1 };
+
+static Family parse_family(const char* family) {
+  if (family == nullptr) return FAM_UNKNOWN;
+  if (strcmp(family, "matmul_lhsT_rhs") == 0) return FAM_LHST;
+  if (strcmp(family, "rmsnorm_matmul") == 0) return FAM_RMSNORM;
+  return FAM_UNKNOWN;
+}
+
+struct Plan {
+  int cta_group;   // 1, or 2 = one UMMA across a CTA pair
+  int m_sub;       // 128-row accumulator blocks per CTA
+  int cluster;     // launch cluster size
+  int tile_m, tile_n, tile_k, stages, group_m;
+  int acc_bufs, tmem_cols;
+  long smem_bytes;
+};
+
+static b200_cfg default_cfg(Family fam) {
+  b200_cfg c;
+  memset(&c, 0, sizeof(c));
+  c.tile_m = 256;
+  c.tile_n = 256;
+  c.tile_k = 64;
+  c.stages = (fam == FAM_RMSNORM) ? 5 : 6;
+  c.cluster_m = 2;
+  c.cluster_n = 1;
+  return c;
+}
+
+static int next_pow2_cols(int cols) {
+  int v = 32;
+  while (v < cols) v <<= 1;
+  return v;
+}
+
+// Validates a candidate and derives the launch plan.  Shape checks are skipped when M == 0.
+static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K, Plan* plan) {
+  if (fam == FAM_UNKNOWN)
+    return set_error(B200_ERR_BAD_ARG, "unknown kernel family (expected matmul_lhsT_rhs or rmsnorm_matmul)");
+  b200_cfg cfg = cfg_in ? *cfg_in : default_cfg(fam);
+  const int cluster_m = cfg.cluster_m == 0 ? 1 : cfg.cluster_m;
+  const int cluster_n = cfg.cluster_n == 0 ? 1 : cfg.cluster_n;
+  if (cfg.tile_m != 128 && cfg.tile_m != 256)
+    return set_error(B200_ERR_UNSUPPORTED, "tile_m=%d: only 128 and 256 are implemented", cfg.tile_m);
+  if (cluster_m != 1 && cluster_m != 2)
+    return set_error(B200_ERR_UNSUPPORTED, "cluster_m=%d: only 1 and 2 are implemented", cluster_m);
+  if (cluster_n != 1)
+    return set_error(B200_ERR_UNSUPPORTED, "cluster_n=%d: only 1 is implemented", cluster_n);
+  Plan p;
+  memset(&p, 0, sizeof(p));
+  p.cluster = cluster_m;
+  p.tile_m = cfg.tile_m;
+  if (cluster_m == 2 && cfg.tile_m == 256) { p.cta_group = 2; p.m_sub = 1; }
+  else if (cfg.tile_m == 256) { p.cta_group = 1; p.m_sub = 2; }
+  else { p.cta_group = 1; p.m_sub = 1; }
+  p.tile_n = cfg.tile_n;
+  p.tile_k = cfg.tile_k;
+  p.stages = cfg.stages;
+  const int nc = cfg.tile_n / p.cta_group;
+  if (cfg.tile_n < 64 || cfg.tile_n > 256 || cfg.tile_n % 32 != 0 || nc % 64 != 0)
+    return set_error(B200_ERR_UNSUPPORTED,
+                     "tile_n=%d: need a multiple of %d in [64,256] (64-column operand chunks per CTA)",
+                     cfg.tile_n, 64 * p.cta_group);
+  if (fam == FAM_RMSNORM ? (cfg.tile_k != 64 && cfg.tile_k != 128)
+                         : (cfg.tile_k != 32 && cfg.tile_k != 64 && cfg.tile_k != 128))
+    return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 are implemented", cfg.tile_k);
+  if (cfg.stages < 1 || cfg.stages > MAX_STAGES)
+    return set_error(B200_ERR_UNSUPPORTED, "stages=%d: need 1..%d", cfg.stages, MAX_STAGES);
+  if (cfg.swizzle < 0 || cfg.swizzle > 64)
+    return set_error(B200_ERR_UNSUPPORTED, "swizzle=%d: need 0..64", cfg.swizzle);
+  p.group_m = cfg.swizzle > 0 ? cfg.swizzle : (p.cta_group == 2 || p.m_sub == 2 ? 8 : 16);
+
+  const int acc_cols = p.m_sub * p.tile_n;
+  p.acc_bufs = (2 * acc_cols <= 512) ? 2 : 1;
+  p.tmem_cols = next_pow2_cols(acc_cols * p.acc_bufs);
+  const long mc = 128L * p.m_sub;
+  const long stage_bytes = (mc + nc) * p.tile_k * 2L;
+  p.smem_bytes = 1024 + p.stages * stage_bytes + static_cast<long>(sizeof(Ctrl));
+  *plan = p;
+  if (acc_cols > 512)
+    return set_error(B200_ERR_TMEM_OOM, "Out of memory in tmem: accumulator needs %d of 512 columns", acc_cols);
+  if (p.smem_bytes > SMEM_BUDGET)
+    return set_error(B200_ERR_SMEM_OOM,
+                     "Out of memory in smem: %d stages x %ld B + %ld B control = %ld B > %ld B per CTA",
+                     p.stages, stage_bytes, 1024 + static_cast<long>(sizeof(Ctrl)), p.smem_bytes, SMEM_BUDGET);
+  if (M != 0 || N != 0 || K != 0) {
+    if (M <= 0 || N <= 0 || K <= 0) return set_error(B200_ERR_BAD_SHAPE, "empty shape M=%ld N=%ld K=%ld", M, N, K);
+    if (M % 8 != 0 || N % 8 != 0)
+      return set_error(B200_ERR_BAD_SHAPE, "M=%ld and N=%ld must be multiples of 8 (16-byte rows)", M, N);
+    if (fam == FAM_RMSNORM && K % 64 != 0)
+      return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul: K=%ld must be a multiple of 64", K);
+    if (M > (1L << 30) || N > (1L << 30) || K > (1L << 30))
+      return set_error(B200_ERR_BAD_SHAPE, "dimension beyond 2^30");
+  }
+  return B200_OK;
+}
+
+// ---------------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] with `cols` contiguous and a row pitch of ld elements; the box
+// is box_cols x box_rows with the 128-byte swizzle (box_cols * 2 must be 128).
+static int make_tmap_bf16(CUtensorMap* tm, const void* base, long rows, long cols, long ld, int box_cols,
+                          int box_rows, const char* what) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return set_error(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return set_error(B200_ERR_BAD_ARG, "%s: base pointer must be 16-byte aligned", what);
+  if (ld % 8 != 0 || ld < cols)
+    return set_error(B200_ERR_BAD_SHAPE, "%s: leading dimension %ld must be a multiple of 8 and >= %ld", what, ld, cols);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(B200_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, (int)r);
+  return B200_OK;
+}
+
+// ---------------------------------------------------------------------------- launch
+typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+
+static GemmKernelFn pick_kernel(Family fam, const Plan& p) {
+  if (fam == FAM_LHST) {
+    if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, MODE_LHST>;
+    if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, MODE_LHST>;
+    return gemm_tcgen05_kernel<1, 1, MODE_LHST>;
+  }
+  if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, MODE_RMSNORM>;
+  if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, MODE_RMSNORM>;
+  return gemm_tcgen05_kernel<1, 1, MODE_RMSNORM>;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int clock_khz = 0;
+};
+
+static int device_info(DeviceInfo* out) {
+  static DeviceInfo cache[64];
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return set_error(B200_ERR_CUDA, "device ordinal %d out of range", dev);
+  if (cache[dev].sm_count == 0) {
+    int major = 0;
+    rc = check_cuda(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev), "device attribute");
+    if (rc) return rc;
+    if (major != 10)
+      return set_error(B200_ERR_CUDA, "device %d has compute capability %d.x; these kernels are sm_100a only", dev, major);
+    rc = check_cuda(cudaDeviceGetAttribute(&cache[dev].clock_khz, cudaDevAttrClockRate, dev), "device attribute");
+    if (rc) return rc;
+    rc = check_cuda(cudaDeviceGetAttribute(&cache[dev].sm_count, cudaDevAttrMultiProcessorCount, dev), "device attribute");
+    if (rc) return rc;
+  }
+  *out = cache[dev];
+  return B200_OK;
+}
+
+struct LaunchArgs {
+  Family fam;
+  const void* a;
+  const void* b;
+  const void* gamma;
+  void* out;
+  long M, N, K, ld_a, ld_b, ld_out;
+  float eps;
+};
+
+// A prepared launch: tensor maps and parameters are built once and can be replayed.
+struct Prepared {
+  GemmKernelFn fn;
+  CUtensorMap tm_a, tm_b;
+  GemmParams gp;
+  Plan plan;
+  dim3 grid, block;
+  size_t smem;
+};
+
+static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, Prepared* pr) {
+  if (!la.a || !la.b || !la.out) return set_error(B200_ERR_BAD_ARG, "NULL operand pointer");
+  Plan plan;
+  int rc = make_plan(la.fam, cfg, la.M, la.N, la.K, &plan);
+  if (rc) return rc;
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc) return rc;
+  if ((reinterpret_cast<uintptr_t>(la.out) & 15u) != 0 || la.ld_out % 8 != 0 || la.ld_out < la.N)
+    return set_error(B200_ERR_BAD_SHAPE, "out: pointer must be 16-byte aligned and ld_out a multiple of 8 >= N");
+  if (la.gamma && (reinterpret_cast<uintptr_t>(la.gamma) & 15u) != 0)
+    return set_error(B200_ERR_BAD_ARG, "gamma: pointer must be 16-byte aligned");
+
+  const int mc = 128 * plan.m_sub;
+  if (la.fam == FAM_LHST) {
+    rc = make_tmap_bf16(&pr->tm_a, la.a, la.K, la.M, la.ld_a, 64, plan.tile_k, "lhsT");
+  } else {
+    rc = make_tmap_bf16(&pr->tm_a, la.a, la.M, la.K, la.ld_a, 64, mc, "x");
+  }
+  if (rc) return rc;
+  rc = make_tmap_bf16(&pr->tm_b, la.b, la.K, la.N, la.ld_b, 64, plan.tile_k, la.fam == FAM_LHST ? "rhs" : "w");
+  if (rc) return rc;
+
+  GemmParams& gp = pr->gp;
+  memset(&gp, 0, sizeof(gp));
+  gp.M = static_cast<int>(la.M);
+  gp.N = static_cast<int>(la.N);
+  gp.K = static_cast<int>(la.K);
+  gp.tile_n = plan.tile_n;
+  gp.tile_k = plan.tile_k;
+  gp.stages = plan.stages;
+  gp.num_m_tiles = static_cast<int>((la.M + plan.tile_m - 1) / plan.tile_m);
+  gp.num_n_tiles = static_cast<int>((la.N + plan.tile_n - 1) / plan.tile_n);
+  gp.num_k_blocks = static_cast<int>((la.K + plan.tile_k - 1) / plan.tile_k);
+  gp.group_m = plan.group_m;
+  gp.acc_bufs = plan.acc_bufs;
+  gp.tmem_cols = plan.tmem_cols;
+  gp.ld_out = la.ld_out;
+  gp.eps = la.eps;
+  gp.inv_k = 1.0f / static_cast<float>(la.K);
+  gp.out = static_cast<__nv_bfloat16*>(la.out);
+  gp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
+  gp.status = dev_status;
+  long long limit_us = 1000000;  // one second per wait
+  if (cfg && cfg->reserved[1] > 0) limit_us = cfg->reserved[1];
+  gp.timeout_cycles = limit_us * (di.clock_khz > 0 ? di.clock_khz / 1000 : 1900);
+  gp.debug_skip_producer = (cfg && cfg->reserved[0] == 1) ? 1 : 0;
+
+  pr->fn = pick_kernel(la.fam, plan);
+  pr->plan = plan;
+  pr->smem = static_cast<size_t>(plan.smem_bytes);
+  pr->block = dim3(static_cast<unsigned>(gemm_threads(la.fam == FAM_RMSNORM ? MODE_RMSNORM : MODE_LHST)));
+  rc = check_cuda(cudaFuncSetAttribute(reinterpret_cast<const void*>(pr->fn),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pr->smem)),
+                  "cudaFuncSetAttribute(max dynamic shared memory)");
+  if (rc) return rc;
+
+  const long total_tiles = static_cast<long>(gp.num_m_tiles) * gp.num_n_tiles;
+  long groups = di.sm_count / plan.cluster;  // CTA groups (clusters) that fit the machine
+  if (plan.cluster > 1) {
+    cudaLaunchConfig_t qc;
+    memset(&qc, 0, sizeof(qc));
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = static_cast<unsigned>(plan.cluster);
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    qc.gridDim = dim3(static_cast<unsigned>(groups * plan.cluster));
+    qc.blockDim = pr->block;
+    qc.dynamicSmemBytes = pr->smem;
+    qc.attrs = qa;
+    qc.numAttrs = 1;
+    int max_clusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, reinterpret_cast<const void*>(pr->fn), &qc);
+    if (e == cudaSuccess && max_clusters > 0 && max_clusters < groups) groups = max_clusters;
+    (void)cudaGetLastError();
+  }
+  // work units per CTA group: a CTA pair shares one tile, co-scheduled single CTAs take one each
+  const long units = (plan.cta_group == 2) ? total_tiles : (total_tiles + plan.cluster - 1) / plan.cluster;
+  if (groups > units) groups = units;
+  if (groups < 1) groups = 1;
+  pr->grid = dim3(static_cast<unsigned>(groups * plan.cluster));
+  return B200_OK;
+}
+
+static int launch(const Prepared& pr, cudaStream_t stream) {
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.gridDim = pr.grid;
+  lc.blockDim = pr.block;
+  lc.dynamicSmemBytes = pr.smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(pr.plan.cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.gp), "tcgen05 GEMM launch");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// =============================================================================== C ABI
+extern "C" const char* b200_last_error(void) { return g_last_error; }
+extern "C" int b200_abi_version(void) { return B200_ABI_VERSION; }
+
+extern "C" int b200_device_count(int* count) {
+  if (!count) return set_error(B200_ERR_BAD_ARG, "device_count: NULL pointer");
+  *count = 0;
+  cudaError_t e = cudaGetDeviceCount(count);
+  if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) {
+    (void)cudaGetLastError();
+    *count = 0;
+    return B200_OK;
+  }
+  return check_cuda(e, "cudaGetDeviceCount");
+}
+
+extern "C" int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K, long* smem_bytes,
+                              int* tmem_cols) {
+  Plan plan;
+  memset(&plan, 0, sizeof(plan));
+  int rc = make_plan(parse_family(family), cfg, M, N, K, &plan);
+  if (smem_bytes) *smem_bytes = plan.smem_bytes;
+  if (tmem_cols) *tmem_cols = plan.tmem_cols;
+  return rc;
+}
+
+extern "C" size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K) {
+  (void)family; (void)cfg; (void)M; (void)N; (void)K;
+  return 0;
+}
+
+extern "C" int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out, long M, long N, long K,
+                                    long ld_lhsT, long ld_rhs, long ld_out, const b200_cfg* cfg, void* workspace,
+                                    size_t workspace_bytes, int* dev_status, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  LaunchArgs la{FAM_LHST, lhsT, rhs, nullptr, out, M, N, K, ld_lhsT ? ld_lhsT : M, ld_rhs ? ld_rhs : N,
+                ld_out ? ld_out : N, 0.0f};
+  Prepared pr;
+  int rc = prepare(la, cfg, dev_status, &pr);
+  if (rc) return rc;
+  return launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out, long M, long N,
+                                   long K, float eps, const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
+                                   int* dev_status, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  LaunchArgs la{FAM_RMSNORM, x, w, gamma, out, M, N, K, K, N, N, eps};
+  Prepared pr;
+  int rc = prepare(la, cfg, dev_status, &pr);
+  if (rc) return rc;
+  return launch(pr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
+                                int* dev_status, void* flush_buf, size_t flush_bytes, int warmup, int iters,
+                                float* ms_each, void* stream_v) {
+  (void)workspace; (void)workspace_bytes;
+  if (!p || !ms_each || iters <= 0 || warmup < 0) return set_error(B200_ERR_BAD_ARG, "time_kernel: bad arguments");
+  Family fam = parse_family(p->family);
+  if (fam == FAM_UNKNOWN) return set_error(B200_ERR_BAD_ARG, "time_kernel: unknown family");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  LaunchArgs la;
+  la.fam = fam;
+  la.a = p->a; la.b = p->b; la.gamma = p->gamma; la.out = p->out;
+  la.M = p->M; la.N = p->N; la.K = p->K;
+  if (fam == FAM_LHST) {
+    la.ld_a = p->ld_a ? p->ld_a : p->M;
+  } else {
+    la.ld_a = p->ld_a ? p->ld_a : p->K;
+  }
+  la.ld_b = p->ld_b ? p->ld_b : p->N;
+  la.ld_out = p->ld_out ? p->ld_out : p->N;
+  la.eps = p->eps;
+  Prepared pr;
+  int rc = prepare(la, cfg, dev_status, &pr);
+  if (rc) return rc;
+
+  std::vector<cudaEvent_t> ev(2 * static_cast<size_t>(iters), nullptr);
+  for (auto& e : ev) {
+    rc = check_cuda(cudaEventCreate(&e), "cudaEventCreate");
+    if (rc) break;
+  }
+  for (int i = 0; i < warmup && rc == B200_OK; ++i) rc = launch(pr, stream);
+  for (int i = 0; i < iters && rc == B200_OK; ++i) {
+    if (flush_buf && flush_bytes)
+      rc = check_cuda(cudaMemsetAsync(flush_buf, i & 0xff, flush_bytes, stream), "L2 flush memset");
+    if (rc == B200_OK) rc = check_cuda(cudaEventRecord(ev[2 * i], stream), "cudaEventRecord");
+    if (rc == B200_OK) rc = launch(pr, stream);
+    if (rc == B200_OK) rc = check_cuda(cudaEventRecord(ev[2 * i + 1], stream), "cudaEventRecord");
+  }
+  if (rc == B200_OK) rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+  for (int i = 0; i < iters && rc == B200_OK; ++i)
+    rc = check_cuda(cudaEventElapsedTime(&ms_each[i], ev[2 * i], ev[2 * i + 1]), "cudaEventElapsedTime");
+  for (auto& e : ev)
+    if (e) cudaEventDestroy(e);
+  if (rc == B200_OK && dev_status) {
+    int host_status[B200_DEV_STATUS_INTS] = {0};
+    rc = check_cuda(cudaMemcpy(host_status, dev_status, sizeof(host_status), cudaMemcpyDeviceToHost), "status copy");
+    if (rc == B200_OK && host_status[0] != 0)
+      rc = set_error(B200_ERR_DEVICE_WAIT,
+                     "device-side wait expired: role %d barrier %d tile %d k-block %d CTA %d", host_status[1],
+                     host_status[2], host_status[3], host_status[4], host_status[5]);
+  }
+  return rc;
+}

@@ -1,0 +1,40 @@
+"""Shared pytest configuration: the ``gpu`` marker, import paths, and the native library."""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import pytest
+
+REPO = Path(__file__).resolve().parent.parent
+PKG = REPO / "nki-autotune_b200"
+for p in (str(PKG), str(REPO)):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def native_lib():
+    """The built shared library; built on demand when nvcc is present, else the test fails."""
+    from autotune import native
+
+    if not native.LIB_PATH.exists():
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("b200_build", PKG / "build.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
+    return native.load()
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+
+    return np.load(REPO / "tests" / "golden" / "reference_outputs.npz")

@@ -1,0 +1,184 @@
+"""Drop-in boundary on CPU: result types, cache writers, candidate descriptors, budget
+checks, and that the shared library exports every symbol the header declares."""
+
+import json
+import re
+
+import numpy as np
+import pytest
+
+from autotune.runner.candidate import Candidate, enumerate_grid, jobs_from_candidates, parse_source
+from autotune.runner.output import ProfileOutput, write_kernel_sources, write_results_json
+from autotune.runner.types import KernelJob, ProfileResult, make_failure, profiler_percent, resolve_dtype, tensor_inputs
+
+from conftest import REPO
+
+
+def _ok(name, t, mfu, **extra):
+    return ProfileResult(name, "[128, 512] float32", {"total_time": t, "mfu_estimated_percent": mfu, **extra})
+
+
+# ---- behaviour pinned by the reference's test/runner/test_output.py ------------------------
+def test_results_json_has_no_hosts_key(tmp_path):
+    write_results_json(str(tmp_path), num_kernels=1, results=[_ok("k_0.py", 0.001, 0.9)], wallclock_s=1.5)
+    data = json.loads((tmp_path / "results.json").read_text())
+    assert "hosts" not in data["metadata"]
+    assert data["metadata"] == {"num_kernels": 1, "wallclock_s": 1.5}
+    assert data["metrics"]["success"] == 1
+    assert data["kernels"][0]["kernel_name"] == "k_0.py"
+
+
+def test_results_json_sorts_numerically(tmp_path):
+    write_results_json(str(tmp_path), 2, [_ok("kernel_10.py", 0.002, 0.5), _ok("kernel_2.py", 0.001, 0.5)], 1.0)
+    data = json.loads((tmp_path / "results.json").read_text())
+    assert [k["kernel_name"] for k in data["kernels"]] == ["kernel_2.py", "kernel_10.py"]
+
+
+def test_profile_output_str():
+    out = ProfileOutput([_ok("k_0.py", 0.001, 0.9)], {}, 2.0, "")
+    text = str(out)
+    assert "Hosts:" not in text and "Succeeded:  1/1" in text and "90.00%" in text
+
+
+# ---- further behaviour of the same module ---------------------------------------------------
+def test_results_json_schema_and_counters(tmp_path):
+    results = [
+        _ok("m_0.py", 0.002, 0.4, mbu_estimated_percent=0.1, mfu_max_achievable_estimated_percent=1.0),
+        _ok("m_1.py", 0.001, 0.8),
+        make_failure("m_2.py", "Out of memory in smem: 5 stages ..."),
+        make_failure("m_3.py", "Out of memory in tmem: ..."),
+        make_failure("m_4.py", "Out of memory in sbuf"),
+        ProfileResult("m_5.py", "[1, 1] x", {"total_time": None, "mfu_estimated_percent": -1.0}),
+    ]
+    write_results_json(str(tmp_path), 6, results, 3.0)
+    data = json.loads((tmp_path / "results.json").read_text())
+    m = data["metrics"]
+    assert (m["success"], m["smem_oom"], m["tmem_oom"], m["sbuf_oom"], m["psum_oom"]) == (2, 1, 1, 1, 0)
+    assert m["best_kernel"] == "m_1.py" and m["worst_kernel"] == "m_0.py"
+    assert m["best_total_time_s"] == 0.001 and m["best_mfu"] == pytest.approx(80.0) and m["best_mbu"] == pytest.approx(10.0)
+    row = data["kernels"][0]
+    assert set(row) == {"kernel_name", "kernel_path", "hardware_output", "total_time_s", "mfu_estimated_percent",
+                        "mbu_estimated_percent", "mfu_max_achievable_estimated_percent"}
+    assert row["kernel_path"] == "m_0/m_0.py"
+    assert json.loads((tmp_path / "m_0" / "profile_summary.json").read_text())["total_time"] == 0.002
+    assert not (tmp_path / "m_2" / "profile_summary.json").exists()
+
+
+def test_success_and_failure_partition():
+    rs = [_ok("a_0.py", 0.1, 0.5), make_failure("a_1.py", "Traceback ..."),
+          ProfileResult("a_2.py", "[1] f", {"total_time": 0.1, "mfu_estimated_percent": -0.5})]
+    out = ProfileOutput(rs, {}, 1.0)
+    assert [s.kernel_name for s in out.successes] == ["a_0.py"]
+    assert [f.kernel_name for f in out.failures] == ["a_1.py"]
+    assert "1 failures:" in str(out)
+
+
+def test_types_helpers():
+    assert profiler_percent({"x": 0.25}, "x") == 25.0
+    assert profiler_percent({"x": -1}, "x") is None and profiler_percent(None, "x") is None
+    assert resolve_dtype("bfloat16").itemsize == 2 and resolve_dtype("float32") == np.float32
+    assert len(tensor_inputs({"a": np.zeros((2, 2)), "s": 3.0, "b": np.zeros(3)})) == 2
+    job = KernelJob("src", "f", (1, 2), {"a": ((1, 2), "float32")})
+    assert job.neuronx_cc_args == () and job.lnc == 1
+
+
+def test_write_kernel_sources(tmp_path):
+    jobs = jobs_from_candidates(enumerate_grid("matmul_lhsT_rhs")[:2], (256, 256),
+                                {"lhs_T": ((128, 256), "bfloat16"), "rhs": ((128, 256), "bfloat16")})
+    write_kernel_sources(str(tmp_path), jobs)
+    text = (tmp_path / "matmul_lhsT_rhs_1" / "matmul_lhsT_rhs_1.py").read_text()
+    assert parse_source(text).family == "matmul_lhsT_rhs"
+
+
+# ---- candidate descriptors -------------------------------------------------------------------
+def test_candidate_round_trip_and_grid():
+    c = Candidate("rmsnorm_matmul", {"tile_m": 128, "tile_n": 256, "tile_k": 64, "stages": 4}, {"eps": 1e-6})
+    back = parse_source(c.to_source())
+    assert back.family == c.family and back.config["tile_n"] == 256 and back.scalars == {"eps": 1e-6}
+    assert back.config["cluster_m"] == 1
+    grid = enumerate_grid("matmul_lhsT_rhs")
+    assert len(grid) == 64 and len({tuple(sorted(g.config.items())) for g in grid}) == 64
+    with pytest.raises(ValueError):
+        parse_source("FAMILY = 'nope'\n")
+    with pytest.raises(ValueError):
+        parse_source("def f(:\n")
+
+
+# ---- native library: exports + budget checks (no GPU needed) ---------------------------------
+def test_library_exports_every_declared_symbol(native_lib):
+    header = (REPO / "include" / "b200_autotune.h").read_text()
+    declared = set(re.findall(r"^(?:int|size_t|const char\*)\s+(b200_\w+)\s*\(", header, flags=re.M))
+    from autotune import native
+
+    assert declared == set(native.SIGNATURES), declared ^ set(native.SIGNATURES)
+    for name in declared:
+        assert hasattr(native_lib, name), name
+    assert native_lib.b200_abi_version() == 1
+
+
+def test_cfg_check_budgets(native_lib):
+    from autotune import native
+
+    ok = native.cfg_check("matmul_lhsT_rhs", dict(tile_m=128, tile_n=256, tile_k=64, stages=4, cluster_m=1), 8192, 8192, 8192)
+    assert ok[0] == native.OK and ok[2] <= 232448 and ok[3] == 512
+    oom = native.cfg_check("matmul_lhsT_rhs", dict(tile_m=128, tile_n=256, tile_k=64, stages=5, cluster_m=1), 8192, 8192, 8192)
+    assert oom[0] == native.ERR_SMEM_OOM and "Out of memory in smem" in oom[1] and oom[2] > 232448
+    assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=96, tile_n=256, tile_k=64, stages=4))[0] == native.ERR_UNSUPPORTED
+    assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=128, tile_n=256, tile_k=64, stages=4), 100, 64, 64)[0] == native.ERR_BAD_SHAPE
+    assert native.cfg_check("nope", None)[0] == native.ERR_BAD_ARG
+    assert native.cfg_check("rmsnorm_matmul", None, 4096, 11008, 4096)[0] == native.OK
+    accepted = sum(native.cfg_check("matmul_lhsT_rhs", c.config, 8192, 8192, 8192)[0] == native.OK
+                   for c in enumerate_grid("matmul_lhsT_rhs"))
+    assert 0 < accepted < 64  # the grid holds both runnable and over-subscribed points
+
+
+def test_compile_one_reports_rejections(native_lib, tmp_path):
+    from autotune.runner.compile import compile_one
+
+    good = Candidate("matmul_lhsT_rhs", dict(tile_m=128, tile_n=128, tile_k=64, stages=3, cluster_m=1))
+    bad = Candidate("matmul_lhsT_rhs", dict(tile_m=256, tile_n=256, tile_k=128, stages=6, cluster_m=1))
+    shapes = {"lhs_T": (512, 256), "rhs": (512, 384)}
+    for i, (cand, expect_err) in enumerate([(good, False), (bad, True)]):
+        p = tmp_path / f"c_{i}.py"
+        p.write_text(cand.to_source())
+        cr = compile_one(f"c_{i}.py", str(p), "matmul_lhsT_rhs", shapes, "bfloat16", (256, 384), log_path=str(tmp_path / f"log{i}.txt"))
+        assert bool(cr.error) == expect_err
+        assert ("rejected" if expect_err else "accepted") in (tmp_path / f"log{i}.txt").read_text()
+    p = tmp_path / "c_9.py"
+    p.write_text(good.to_source())
+    cr = compile_one("c_9.py", str(p), "matmul_lhsT_rhs", {"lhs_T": (512, 256), "rhs": (500, 384)}, "bfloat16", (256, 384))
+    assert "do not match" in cr.error
+
+
+def test_kernels_refuse_cpu_tensors(native_lib):
+    import torch
+
+    from autotune import kernels
+    from autotune.native import NativeError
+
+    a = torch.zeros(64, 64, dtype=torch.bfloat16)
+    with pytest.raises(NativeError):
+        kernels.matmul_lhsT_rhs(a, a)
+    with pytest.raises(NativeError):
+        kernels.rmsnorm_matmul(a, None, a)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from autotune import native
+
+    monkeypatch.setattr(native, "_lib", None)
+    monkeypatch.setenv("B200_AUTOTUNE_LIB", str(tmp_path / "absent.so"))
+    with pytest.raises(native.NativeError, match="no CPU fallback"):
+        native.load()
+
+
+def test_generate_tensors_follows_reference_recipe():
+    from autotune.runner.benchmark import generate_tensors
+
+    specs = {"lhs_T": {"shape": [8, 4], "dtype": "float32"}, "rhs": {"shape": [8, 6], "dtype": "bfloat16"},
+             "g": {"shape": [6], "dtype": "float32", "dist": {"kind": "uniform", "low": 0.5, "high": 1.5}}}
+    got = generate_tensors(specs, 7)
+    rng = np.random.default_rng(7)
+    assert np.array_equal(got["lhs_T"], rng.standard_normal((8, 4)).astype(np.float32))
+    assert np.array_equal(got["rhs"], rng.standard_normal((8, 6)).astype(resolve_dtype("bfloat16")))
+    assert np.array_equal(got["g"], rng.uniform(0.5, 1.5, (6,)).astype(np.float32))
