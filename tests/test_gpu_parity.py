@@ -1,0 +1,223 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI (GPU box only).
+
+Tolerances: max |a-e| / (|e| + rms(e)) <= 1e-2 for bf16 inputs with fp32 accumulation and
+bf16 output; <= 1e-5 for the fp32 configuration.
+"""
+
+import ml_dtypes
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 1e-2
+TOL_FP32 = 1e-5
+U = {"kind": "uniform", "low": 0.5, "high": 1.5}
+BF = ml_dtypes.bfloat16
+
+
+def N_(k):
+    return {"kind": "normal", "scale": k ** -0.5}
+
+
+def cfg(tm, tn, tk, st, cm=1, sw=0):
+    return dict(tile_m=tm, tile_n=tn, tile_k=tk, stages=st, cluster_m=cm, swizzle=sw)
+
+
+@pytest.fixture(scope="module")
+def K(native_lib):
+    import torch
+
+    assert torch.cuda.is_available()
+    from autotune import kernels
+
+    return kernels
+
+
+def _mm_case(K, seed, k, m, n, c):
+    t = O.generate_inputs(seed, [("lhs_T", (k, m), N_(k)), ("rhs", (k, n), N_(k))], bf16=True)
+    got = K.matmul_lhsT_rhs_host(t["lhs_T"].astype(BF), t["rhs"].astype(BF), c).astype(np.float32)
+    return O.max_abs_rel_err(got, O.matmul_lhsT_rhs(t["lhs_T"], t["rhs"]))
+
+
+# ---- fp32 configuration ----------------------------------------------------------------------
+def test_fp32_config_512_matches_golden(K, golden):
+    c = O.config_specs("cfg1_fp32_512")
+    t = O.generate_inputs(c["seed"], c["specs"], c["bf16"])
+    got = K.matmul_lhsT_rhs_host(t["lhs_T"], t["rhs"])
+    assert O.max_abs_rel_err(got, golden["matmul_512_seed0"]) <= TOL_FP32
+    assert O.max_abs_rel_err(got, O.matmul_lhsT_rhs(t["lhs_T"], t["rhs"])) <= TOL_FP32
+
+
+def test_fp32_reference_op_case_128(K, golden):
+    t = O.generate_inputs(0, [("lhs_T", (128, 128), None), ("rhs", (128, 128), None)], bf16=False)
+    got = K.matmul_lhsT_rhs_host(t["lhs_T"], t["rhs"])
+    assert np.allclose(got, golden["matmul_128_seed0"], atol=1e-4, rtol=1e-4)  # the reference's own tolerance
+
+
+@pytest.mark.parametrize("k,m,n", [(1, 1, 1), (7, 13, 5), (300, 200, 136), (16, 65, 129)])
+def test_fp32_ragged_shapes(K, k, m, n):
+    t = O.generate_inputs(11, [("lhs_T", (k, m), None), ("rhs", (k, n), None)], bf16=False)
+    got = K.matmul_lhsT_rhs_host(t["lhs_T"], t["rhs"])
+    assert O.max_abs_rel_err(got, O.matmul_lhsT_rhs(t["lhs_T"], t["rhs"])) <= TOL_FP32
+
+
+# ---- tcgen05 GEMM ----------------------------------------------------------------------------
+def test_bf16_golden_case(K, golden):
+    t = O.generate_inputs(1, [("lhs_T", (384, 256), N_(384)), ("rhs", (384, 320), N_(384))], bf16=True)
+    got = K.matmul_lhsT_rhs_host(t["lhs_T"].astype(BF), t["rhs"].astype(BF), cfg(128, 64, 64, 3)).astype(np.float32)
+    assert O.max_abs_rel_err(got, golden["matmul_bf16in_384x256x320_seed1"]) <= TOL_BF16
+
+
+GRID = [cfg(tm, tn, tk, st, cm)
+        for tm in (128, 256) for tn in (128, 256) for tk in (64, 128) for st in (3, 4) for cm in (1, 2)]
+
+
+@pytest.mark.parametrize("c", GRID, ids=lambda c: f"{c['tile_m']}x{c['tile_n']}x{c['tile_k']}s{c['stages']}c{c['cluster_m']}")
+def test_bf16_every_tile_candidate_small(K, c):
+    """256x256x512 (the reference's cheap fixture shape family) for every point of the tile grid."""
+    from autotune import native
+
+    status, msg, _, _ = native.cfg_check("matmul_lhsT_rhs", c, 512, 512, 512)
+    if status != native.OK:
+        assert status in (native.ERR_SMEM_OOM, native.ERR_TMEM_OOM), msg
+        with pytest.raises(native.NativeError):
+            _mm_case(K, 5, 512, 512, 512, c)
+        return
+    assert _mm_case(K, 5, 512, 512, 512, c) <= TOL_BF16
+
+
+@pytest.mark.parametrize("k,m,n", [(64, 128, 64), (8, 8, 8), (72, 136, 200), (520, 1000, 1016), (2048, 2048, 2048), (1000, 264, 72)])
+@pytest.mark.parametrize("c", [cfg(128, 128, 64, 4), cfg(256, 128, 64, 4, cm=2), cfg(256, 128, 64, 3)],
+                         ids=["1cta", "pair", "msub2"])
+def test_bf16_edges_and_sizes(K, k, m, n, c):
+    assert _mm_case(K, 6, k, m, n, c) <= TOL_BF16
+
+
+def test_bf16_hand_kernel_shape_2048(K, golden):
+    """2048^3, the only shape the reference's hand kernel accepts, against its simulated output."""
+    t = O.generate_inputs(0, [("lhs_T", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
+    got = K.matmul_lhsT_rhs_host(t["lhs_T"].astype(BF), t["rhs"].astype(BF)).astype(np.float32)
+    assert O.max_abs_rel_err(got, O.matmul_lhsT_rhs(t["lhs_T"], t["rhs"])) <= TOL_BF16
+    # the golden was computed from unrounded fp32 inputs: bf16 input rounding adds ~2^-9 relative noise per term
+    sample, ref = got[::127, ::131], golden["hand_matmul_2048_seed0_sample"]
+    assert np.max(np.abs(sample - ref)) / np.sqrt(np.mean(ref * ref)) <= 3e-2
+
+
+def test_strided_operands(K):
+    """A column slice of lhsT (the large-M shard case) and a padded output, no copies."""
+    import torch
+
+    k, m_total, n = 256, 1024, 256
+    t = O.generate_inputs(8, [("lhs_T", (k, m_total), N_(k)), ("rhs", (k, n), N_(k))], bf16=True)
+    a = K.to_device(t["lhs_T"].astype(BF))
+    b = K.to_device(t["rhs"].astype(BF))
+    out = torch.zeros(m_total, n + 64, dtype=torch.bfloat16, device="cuda")
+    for g in range(4):
+        K.matmul_lhsT_rhs(a[:, g * 256:(g + 1) * 256], b, cfg=cfg(128, 128, 64, 3), out=out[g * 256:(g + 1) * 256, :n])
+    torch.cuda.synchronize()
+    got = K.to_host(out).astype(np.float32)
+    assert O.max_abs_rel_err(got[:, :n], O.matmul_lhsT_rhs(t["lhs_T"], t["rhs"])) <= TOL_BF16
+    assert not got[:, n:].any()  # padding untouched
+
+
+def test_linearity_and_determinism_full_size(K):
+    """Size-independent properties at 8192^3: C(a, 2b) = 2 C(a, b) exactly in bf16 (power-of-two
+    scale), and two launches agree bit for bit."""
+    import torch
+
+    torch.manual_seed(1)
+    a = (torch.randn(8192, 8192, device="cuda") * 8192 ** -0.5).bfloat16()
+    b = (torch.randn(8192, 8192, device="cuda") * 8192 ** -0.5).bfloat16()
+    c1 = K.matmul_lhsT_rhs(a, b)
+    c2 = K.matmul_lhsT_rhs(a, b)
+    c3 = K.matmul_lhsT_rhs(a, b * 2)
+    torch.cuda.synchronize()
+    assert torch.equal(c1, c2)
+    assert torch.equal(c3, c1 * 2)
+    # column-sum checksum against an fp32 evaluation: sum_m C[m, n] = (sum_m lhsT[:, m]) . rhs[:, n]
+    ref = (a.float().sum(dim=1) @ b.float())
+    got = c1.float().sum(dim=0)
+    assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
+
+
+# ---- fused RMSNorm + matmul ------------------------------------------------------------------
+def _rms_case(K, seed, m, k, n, eps, c, gamma=True):
+    t = O.generate_inputs(seed, [("x", (m, k), None), ("gamma", (k,), U), ("weight", (k, n), N_(k))], bf16=True)
+    g = t["gamma"] if gamma else None
+    got = K.rmsnorm_matmul_host(t["x"].astype(BF), g.astype(BF) if gamma else None, t["weight"].astype(BF), eps, c)
+    return got.astype(np.float32), O.rmsnorm_matmul(t["x"], g, t["weight"], eps)
+
+
+@pytest.mark.parametrize("key,seed,m,k,n,eps", [("rmsnorm_gamma_256x512x384_seed2", 2, 256, 512, 384, 1e-6),
+                                                ("rmsnorm_gamma_16x1024x512_seed3", 3, 16, 1024, 512, 1e-5)])
+@pytest.mark.parametrize("c", [cfg(128, 128, 64, 3), cfg(128, 128, 128, 2), cfg(256, 128, 64, 3), cfg(256, 128, 64, 3, cm=2)],
+                         ids=["1cta", "tk128", "msub2", "pair"])
+def test_rmsnorm_golden_cases(K, golden, key, seed, m, k, n, eps, c):
+    got, expect = _rms_case(K, seed, m, k, n, eps, c)
+    assert O.max_abs_rel_err(got, golden[key]) <= TOL_BF16
+    assert O.max_abs_rel_err(got, expect) <= TOL_BF16
+
+
+def test_rmsnorm_without_gamma_is_reference_kernel_maths(K, golden):
+    t = O.generate_inputs(0, [("lhs", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
+    got = K.rmsnorm_matmul_host(t["lhs"].astype(BF), None, t["rhs"].astype(BF), 1e-6).astype(np.float32)
+    assert O.max_abs_rel_err(got, O.rmsnorm_matmul(t["lhs"], None, t["rhs"], 1e-6)) <= TOL_BF16
+    sample, ref = got[::127, ::131], golden["hand_rmsnorm_2048_seed0_sample"]
+    assert np.max(np.abs(sample - ref)) / np.sqrt(np.mean(ref * ref)) <= 3e-2
+
+
+def test_rmsnorm_row_scale_invariance(K):
+    """rmsnorm(c * x) = rmsnorm(x) for c a power of two (eps negligible): outputs agree closely."""
+    g1, _ = _rms_case(K, 9, 256, 512, 256, 1e-12, cfg(128, 128, 64, 3))
+    t = O.generate_inputs(9, [("x", (256, 512), None), ("gamma", (512,), U), ("weight", (512, 256), N_(512))], bf16=True)
+    got4 = K.rmsnorm_matmul_host((t["x"] * 4).astype(BF), t["gamma"].astype(BF), t["weight"].astype(BF), 1e-12,
+                                 cfg(128, 128, 64, 3)).astype(np.float32)
+    assert O.max_abs_rel_err(got4, g1) <= 1e-2
+
+
+def test_fused_matches_fp32_device_crosscheck(K):
+    import torch
+
+    t = O.generate_inputs(4, [("x", (512, 1024), None), ("gamma", (1024,), U), ("weight", (1024, 768), N_(1024))], bf16=True)
+    x, g, w = (K.to_device(t[k].astype(BF)) for k in ("x", "gamma", "weight"))
+    ref = K.rmsnorm_matmul_f32(x, g, w, 1e-6)
+    out = K.rmsnorm_matmul(x, g, w, 1e-6, cfg(128, 256, 64, 4))
+    torch.cuda.synchronize()
+    assert O.max_abs_rel_err(K.to_host(ref), O.rmsnorm_matmul(t["x"], t["gamma"], t["weight"], 1e-6)) <= 1e-4
+    assert O.max_abs_rel_err(K.to_host(out).astype(np.float32), K.to_host(ref)) <= TOL_BF16
+
+
+# ---- argument checking and bounded waits -------------------------------------------------------
+def test_bad_arguments_raise(K):
+    import torch
+
+    from autotune.native import NativeError
+
+    a = torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NativeError):
+        K.matmul_lhsT_rhs(a, torch.zeros(32, 128, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(NativeError):
+        K.matmul_lhsT_rhs(a, a, cfg=cfg(128, 128, 64, 99))
+    with pytest.raises(NativeError):
+        K.matmul_lhsT_rhs(torch.zeros(64, 100, dtype=torch.bfloat16, device="cuda"), a)  # M not a multiple of 8
+
+
+def test_wait_that_runs_out_reports_status_and_context_survives(K):
+    """A producer that issues nothing makes the consumer's bounded wait expire: the launch ends,
+    the status block names the wait, and the next launch on the same context is correct."""
+    import torch
+
+    from autotune.native import NativeError
+
+    a = torch.ones(128, 256, dtype=torch.bfloat16, device="cuda")
+    st = K.new_status()
+    c = cfg(128, 128, 64, 3)
+    c.update(_debug_skip_producer=1, _wait_limit_us=2000)
+    K.matmul_lhsT_rhs(a, a, cfg=c, status=st)
+    with pytest.raises(NativeError, match="wait expired"):
+        K.raise_on_status(st)
+    assert st.cpu()[0].item() == 7
+    assert _mm_case(K, 3, 256, 256, 256, cfg(128, 128, 64, 3)) <= TOL_BF16
