@@ -1,0 +1,501 @@
+"""Benchmark of the hot path on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+A step is one launch of the autotuned bf16 ``matmul_lhsT_rhs`` kernel at 8192^3 (fp32
+accumulation, bf16 output; 1.0995e12 FLOP, 4.03e8 algorithmic bytes).  With N > 1 (one rank per
+GPU, launched by ``torch.distributed.run``) every rank runs the same per-GPU problem -- the row
+split of a [K=8192, M=8192*N] lhsT with rhs replicated -- so scaling is weak, there is no
+data-path collective, and ``value`` is the total FLOP of all ranks over the slowest rank's time.
+Host-side rendezvous (barrier, max, gather) uses gloo.  Rank 0 prints one JSON line.
+
+``--impl reference`` times the reference's CPU path for the same contraction (the numpy
+restatement in ``oracle/``; the reference's simulator is a BLAS sgemm per matmul op) on the
+host cores, each step a bounded sample of the workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+for _p in (str(REPO / "nki-autotune_b200"), str(REPO)):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+M = N = K = 8192
+FLOPS_PER_STEP = 2.0 * M * N * K
+ALGO_BYTES_PER_STEP = 3.0 * M * N * 2  # lhsT + rhs read once, C written once (bf16)
+METRIC = "bf16 TFLOP/s matmul_lhsT_rhs 8192^3 (autotuned, fp32 accumulate, bf16 out)"
+WORKLOAD = "configs[1]: matmul_lhsT_rhs bf16 lhsT[8192,8192] rhs[8192,8192], N(0,1)/sqrt(K), seed 1"
+
+# DRAM bytes per launch of the 8192^3 kernel (dram__bytes_read.sum + dram__bytes_write.sum);
+# filled from the ncu capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+SHORTLIST = [
+    dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2),
+    dict(tile_m=256, tile_n=256, tile_k=64, stages=6, cluster_m=2),
+    dict(tile_m=128, tile_n=256, tile_k=128, stages=2, cluster_m=1),
+    dict(tile_m=128, tile_n=256, tile_k=64, stages=4, cluster_m=1),
+]
+
+
+def env_int(name: str, default: int) -> int:
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()  # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c in sm if c > 0.5 * max(sm)] if sm else []
+        return {
+            "sm_mhz": statistics.median(busy) if busy else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+class Ranks:
+    """Host-side rendezvous over gloo (nothing on the kernel path uses a collective)."""
+
+    def __init__(self):
+        self.rank = env_int("RANK", 0)
+        self.world = env_int("WORLD_SIZE", 1)
+        self.local_rank = env_int("LOCAL_RANK", 0)
+        self.dist = None
+        if self.world > 1:
+            import datetime
+
+            import torch.distributed as dist
+
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("gloo", rank=self.rank, world_size=self.world,
+                                    timeout=datetime.timedelta(seconds=600))
+            self.dist = dist
+
+    def barrier(self) -> None:
+        if self.dist is not None:
+            self.dist.barrier()
+
+    def max(self, value: float) -> float:
+        if self.dist is None:
+            return value
+        import torch
+
+        t = torch.tensor([value], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def gather(self, obj):
+        if self.dist is None:
+            return [obj]
+        out = [None] * self.world if self.rank == 0 else None
+        self.dist.gather_object(obj, out, dst=0)
+        return out
+
+    def close(self) -> None:
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+def make_inputs():
+    """Config-2 inputs as bf16 numpy arrays (host memory), per the oracle's recipe."""
+    import ml_dtypes
+
+    from oracle import oracle as O
+
+    cfg = O.config_specs("cfg2_bf16_8192")
+    t = O.generate_inputs(cfg["seed"], cfg["specs"], bf16=False)
+    return t["lhs_T"].astype(ml_dtypes.bfloat16), t["rhs"].astype(ml_dtypes.bfloat16)
+
+
+def pick_config(kernels, a, b, out, status) -> tuple[dict, dict]:
+    """Untimed mini-sweep over a short list; returns (best config, {config-name: ms})."""
+    from autotune import native
+
+    seen = {}
+    best, best_ms = None, float("inf")
+    for cfg in SHORTLIST:
+        if native.cfg_check("matmul_lhsT_rhs", cfg, M, N, K)[0] != native.OK:
+            continue
+        ms = kernels.time_kernel("matmul_lhsT_rhs", a, b, out, cfg, warmup=2, iters=5, status=status)
+        med = statistics.median(ms)
+        seen["{tile_m}x{tile_n}x{tile_k}s{stages}c{cluster_m}".format(**cfg)] = round(med, 4)
+        if med < best_ms:
+            best, best_ms = cfg, med
+    return best, seen
+
+
+def timed_region(ranks: Ranks, torch, body, steps: int) -> float:
+    """barrier + synchronize, `steps` x body() between two CUDA events on the current stream,
+    synchronize + barrier; returns the max-over-ranks milliseconds per step."""
+    torch.cuda.synchronize()
+    ranks.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        body()
+    e1.record()
+    torch.cuda.synchronize()
+    ranks.barrier()
+    return ranks.max(e0.elapsed_time(e1) / steps)
+
+
+def cpu_baseline_sample(lhs_T_bf16, rhs_bf16, sample_cols: int) -> tuple[float, float, "object"]:
+    """Times the CPU oracle on lhsT[:, :sample_cols] (a row block of C); returns (s, TFLOP/s, C block)."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    a = np.ascontiguousarray(lhs_T_bf16[:, :sample_cols]).astype(np.float32)
+    b = rhs_bf16.astype(np.float32)
+    O.matmul_lhsT_rhs(a[:, :256], b)  # warm the BLAS threads
+    t0 = time.perf_counter()
+    c = O.matmul_lhsT_rhs(a, b)
+    dt = time.perf_counter() - t0
+    return dt, 2.0 * sample_cols * N * K / dt / 1e12, c
+
+
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+
+    from autotune import kernels, native
+    from autotune.peaks import load_peaks
+    from oracle import oracle as O
+
+    native.load()
+    ranks = Ranks()
+    torch.cuda.set_device(ranks.local_rank)
+    lhs_T_np, rhs_np = make_inputs()
+    a_host = torch.from_numpy(lhs_T_np.view(np.uint16)).view(torch.bfloat16).pin_memory()
+    b_host = torch.from_numpy(rhs_np.view(np.uint16)).view(torch.bfloat16).pin_memory()
+    c_host = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    a = a_host.cuda(non_blocking=True)
+    b = b_host.cuda(non_blocking=True)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    status = kernels.new_status()
+    torch.cuda.synchronize()
+
+    cfg, shortlist_ms = pick_config(kernels, a, b, out, status)
+
+    def step():
+        kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=out, status=status)
+
+    def step_e2e():
+        a.copy_(a_host, non_blocking=True)
+        b.copy_(b_host, non_blocking=True)
+        kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=out, status=status)
+        c_host.copy_(out, non_blocking=True)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(physical_gpu_index(ranks.local_rank))
+    sampler.start()
+    ms_step = timed_region(ranks, torch, step, args.steps)
+    clocks = sampler.stop()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed_region(ranks, torch, step_e2e, args.steps)
+    kernels.raise_on_status(status)
+
+    peaks = load_peaks()
+    total_flops = FLOPS_PER_STEP * ranks.world
+    value = total_flops / (ms_step * 1e-3) / 1e12
+    achieved = FLOPS_PER_STEP / (ms_step * 1e-3) / 1e12
+    line = {
+        "metric": METRIC,
+        "value": round(value, 2),
+        "unit": "TFLOP/s",
+        "n_gpus": ranks.world,
+        "steps": args.steps,
+        "warmup": max(3, args.warmup),
+        "ms_per_step": round(ms_step, 5),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": WORKLOAD,
+            "per_gpu": "M=N=K=8192 (rows of a [8192*n_gpus]-row product, rhs replicated)",
+            "kernel_config": cfg,
+            "shortlist_ms": shortlist_ms,
+            "l2": "inputs+output 384 MiB per launch exceed the 126 MB L2; no flush between steps",
+            "peaks": peaks["source"],
+        },
+        "roofline": {
+            "bound": "tensor",
+            "achieved": round(achieved, 2),
+            "peak": peaks["bf16_tflops"],
+            "unit": "TFLOP/s",
+            "frac": round(achieved / peaks["bf16_tflops"], 4),
+            "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+            "frac_of_sustained_peak": round(achieved / peaks["bf16_tflops_sustained"], 4),
+        },
+        "e2e": {
+            "value": round(total_flops / (ms_e2e * 1e-3) / 1e12, 2),
+            "unit": "TFLOP/s",
+            "ms_per_step": round(ms_e2e, 4),
+            "h2d_bytes_per_step": int(a_host.numel() * 2 + b_host.numel() * 2),
+            "d2h_bytes_per_step": int(c_host.numel() * 2),
+        },
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+    }
+
+    if ranks.rank == 0 and ranks.world == 1:
+        # parity of what was just timed, and the CPU baseline on a bounded sample (2048 of 8192 rows)
+        sample = 2048
+        dt, tflops, c_cpu = cpu_baseline_sample(lhs_T_np, rhs_np, sample)
+        got = c_host[:sample].view(torch.uint16).numpy().view(lhs_T_np.dtype).astype(np.float32)
+        line["cpu_baseline"] = {
+            "value": round(tflops, 4), "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"rows 0..{sample - 1} of C (lhsT[:, :{sample}]^T . rhs, fp32 BLAS), {dt:.2f} s, 1 repetition",
+        }
+        line["parity"] = {"max_abs_rel_err": float(f"{O.max_abs_rel_err(got, c_cpu):.3e}"), "tol": 1e-2,
+                          "checked": f"{sample}x{N} outputs of the e2e result against the CPU oracle"}
+    if not args.no_extras:
+        try:
+            extras = run_extras(ranks, torch, kernels, args)
+        except Exception as exc:  # noqa: BLE001 - extras never take the headline down
+            extras = {"error": repr(exc)}
+        if ranks.rank == 0:
+            line["extras"] = extras
+    if ranks.rank == 0:
+        print(json.dumps(line), flush=True)
+    ranks.close()
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    ids = [v.strip() for v in vis.split(",") if v.strip()]
+    if ids and local_rank < len(ids) and ids[local_rank].isdigit():
+        return int(ids[local_rank])
+    return local_rank
+
+
+def _time_family(kernels, family, a, b, out, cfg, gamma=None, eps=0.0, iters=10, flush=None):
+    ms = kernels.time_kernel(family, a, b, out, cfg, gamma=gamma, eps=eps, warmup=3, iters=iters, flush=flush)
+    return statistics.median(ms)
+
+
+def run_extras(ranks: Ranks, torch, kernels, args) -> dict:
+    """Secondary configurations, device-generated inputs, kernel time only (CUDA events)."""
+    from autotune.peaks import load_peaks
+
+    peaks = load_peaks()
+    extras: dict = {}
+    g = torch.Generator(device="cuda").manual_seed(1234 + ranks.rank)
+
+    def randn(*shape, scale=1.0):
+        return (torch.randn(*shape, device="cuda", generator=g) * scale).bfloat16()
+
+    if ranks.world == 1:
+        # configs[2]: fused RMSNorm + matmul against the plain GEMM at the same shape
+        Mx, Kx, Nx = 4096, 4096, 11008
+        x, w = randn(Mx, Kx), randn(Kx, Nx, scale=Kx ** -0.5)
+        gamma = (torch.rand(Kx, device="cuda", generator=g) + 0.5).bfloat16()
+        o = torch.empty(Mx, Nx, dtype=torch.bfloat16, device="cuda")
+        xt = x.t().contiguous()
+        cfg = dict(tile_m=256, tile_n=256, tile_k=64, stages=5, cluster_m=2)
+        fused = _time_family(kernels, "rmsnorm_matmul", x, w, o, cfg, gamma=gamma, eps=1e-6)
+        ref = kernels.rmsnorm_matmul_f32(x[:256], gamma, w, 1e-6)
+        err = float(((o[:256].float() - ref).abs() / (ref.abs() + ref.pow(2).mean().sqrt())).max())
+        plain = _time_family(kernels, "matmul_lhsT_rhs", xt, w, o, dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2))
+        fl = 2.0 * Mx * Nx * Kx
+        extras["rmsnorm_matmul_4096x11008x4096"] = {
+            "fused_ms": round(fused, 4), "plain_gemm_ms": round(plain, 4), "fused_over_plain": round(fused / plain, 3),
+            "fused_tflops": round(fl / fused / 1e9, 1), "max_abs_rel_err_vs_fp32_kernel_256_rows": float(f"{err:.3e}"),
+        }
+        del x, w, o, xt
+        # configs[3]: skinny decode shape, memory bound
+        Mx, Kx, Nx = 16, 8192, 28672
+        x, w = randn(Mx, Kx), randn(Kx, Nx, scale=Kx ** -0.5)
+        gamma = (torch.rand(Kx, device="cuda", generator=g) + 0.5).bfloat16()
+        o = torch.empty(Mx, Nx, dtype=torch.bfloat16, device="cuda")
+        ms = _time_family(kernels, "rmsnorm_matmul", x, w, o, dict(tile_m=128, tile_n=256, tile_k=64, stages=4, cluster_m=1),
+                          gamma=gamma, eps=1e-5)
+        nbytes = (Mx * Kx + Kx * Nx + Mx * Nx + Kx) * 2
+        extras["rmsnorm_matmul_skinny_16x28672x8192"] = {
+            "ms": round(ms, 4), "hbm_gbs": round(nbytes / ms / 1e6, 1), "frac_of_hbm_peak": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4),
+            "note": "weights (470 MB) exceed L2",
+        }
+        del x, w, o
+
+    # configs[4]: large-M row split, M=131072 sharded evenly over the ranks (strong scaling)
+    Mt, Kx, Nx = 131072, 4096, 4096
+    m_local = Mt // ranks.world
+    a, b = randn(Kx, m_local, scale=Kx ** -0.5), randn(Kx, Nx, scale=Kx ** -0.5)
+    o = torch.empty(m_local, Nx, dtype=torch.bfloat16, device="cuda")
+    cfg = dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2)
+    for _ in range(3):
+        kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=o)
+    ms = timed_region(ranks, torch, lambda: kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=o), 5)
+    if ranks.rank == 0:
+        extras["large_m_row_split_131072x4096x4096"] = {
+            "n_gpus": ranks.world, "rows_per_gpu": m_local, "ms": round(ms, 4),
+            "aggregate_tflops": round(2.0 * Mt * Nx * Kx / ms / 1e9, 1), "scaling": "strong",
+        }
+    del a, b, o
+
+    # autotune sweep of the 64-point grid at 8192^3, candidates sharded over the ranks
+    if args.sweep:
+        from autotune.runner.api import profile
+        from autotune.runner.candidate import enumerate_grid, jobs_from_candidates
+
+        s = {"kind": "normal", "scale": 8192 ** -0.5}
+        jobs = jobs_from_candidates(
+            enumerate_grid("matmul_lhsT_rhs"), (M, N),
+            {"lhs_T": ((K, M), "bfloat16", s), "rhs": ((K, N), "bfloat16", s)})
+        torch.cuda.synchronize()
+        ranks.barrier()
+        t0 = time.perf_counter()
+        res = profile(jobs, "", 1, "b200", False, warmup=2, iters=5, shard=(ranks.rank, ranks.world))
+        ranks.barrier()
+        wall = ranks.max(time.perf_counter() - t0)
+        rows = ranks.gather([(r.kernel_name, r.total_time_s, r.mfu) for r in res.successes])
+        fails = ranks.gather(len(res.failures))
+        if ranks.rank == 0:
+            flat = sorted((r for part in rows for r in part), key=lambda r: r[1])
+            extras["sweep_64_candidates_8192"] = {
+                "wallclock_s": round(wall, 2), "n_gpus": ranks.world, "succeeded": len(flat), "failed": sum(fails),
+                "best": flat[0] if flat else None,
+            }
+    return extras
+
+
+def run_reference(args) -> None:
+    """The reference's CPU path (one fp32 BLAS matmul per matmul op) on the host cores, rank 0 only."""
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return
+    import numpy as np
+
+    from oracle import oracle as O
+
+    sample = 2048  # columns of lhsT = rows of C per step: a quarter of the 8192^3 workload
+    lhs_T_np, rhs_np = make_inputs()
+    a = np.ascontiguousarray(lhs_T_np[:, :sample]).astype(np.float32)
+    b = rhs_np.astype(np.float32)
+    # bound the whole run to a few minutes whatever --steps says
+    O.matmul_lhsT_rhs(a[:, :256], b)
+    t0 = time.perf_counter()
+    O.matmul_lhsT_rhs(a, b)
+    one = time.perf_counter() - t0
+    budget_s = 150.0
+    while sample > 256 and one * (args.steps + args.warmup) > budget_s:
+        sample //= 2
+        one /= 2
+    a = np.ascontiguousarray(a[:, :sample])
+    for _ in range(args.warmup):
+        O.matmul_lhsT_rhs(a, b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.matmul_lhsT_rhs(a, b)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * sample * N * K / dt / 1e12
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": round(tflops, 4),
+        "unit": "TFLOP/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD,
+                   "note": "CPU path of the reference (numpy restatement of NKIMatmul._run); runs on rank 0's host cores only"},
+        "cpu_baseline": {"value": round(tflops, 4), "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": f"rows 0..{sample - 1} of C per step (lhsT[:, :{sample}]^T . rhs), fp32 BLAS"},
+        "e2e": {"value": round(tflops, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-extras", action="store_true", help="headline only")
+    ap.add_argument("--sweep", action="store_true", help="also time the full 64-candidate sweep (extras)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -29,6 +29,7 @@ def profile(
     n_gpus: int | None = None,
     warmup: int = 3,
     iters: int = 10,
+    shard: tuple[int, int] | None = None,
 ) -> ProfileOutput:
     """Validate and time a set of candidates on the GPUs of this box.
 
@@ -43,6 +44,8 @@ def profile(
         collect_detailed_profile: Attach the per-launch timing list as ``profile.json``.
         n_gpus: Optional cap on the number of GPUs the sweep is sharded over (extension).
         warmup, iters: Untimed and timed launches per candidate (extension).
+        shard: ``(rank, world)`` when the caller already runs one process per GPU; this
+            process then times only its share of the candidates (extension).
 
     Returns:
         ``ProfileOutput`` with every candidate present, as a success or as a failure row.
@@ -64,6 +67,7 @@ def profile(
         n_gpus=n_gpus,
         warmup=warmup,
         iters=iters,
+        shard=shard,
     )
     elapsed_s = time.monotonic() - start
     logger.info("Profile complete: %d results in %.1fs", len(results), elapsed_s)

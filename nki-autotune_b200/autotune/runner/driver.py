@@ -214,7 +214,7 @@ def run_sharded(
                 elif kind == "crash":
                     _fail_current(slot, f"worker crashed:\n{payload}")
                 else:
-                    _fail_current(slot, "worker exited without reporting (pipe closed)")
+                    _fail_current(slot, "worker process died without reporting (pipe closed)")
             elif slot.proc is not None and not slot.proc.is_alive():
                 # drain anything it managed to send before dying
                 if not slot.conn.poll(0):
@@ -249,8 +249,14 @@ def run_pipeline(
     warmup: int = 3,
     iters: int = 10,
     deadline_s: float = DEFAULT_DEADLINE_S,
+    shard: tuple[int, int] | None = None,
 ) -> tuple[list[ProfileResult], dict[str, str]]:
     """Validate + time every candidate; returns ``(results, compiler_logs)``.
+
+    ``shard=(rank, world)`` is for callers that already run one process per GPU (for example
+    under ``torchrun``): this process times only accepted candidates ``rank, rank+world, ...``
+    on its current device and returns their rows (rank 0 also returns the rejected ones); the
+    caller gathers the per-rank lists on the host.
 
     ``n_gpus`` (or the environment variable ``B200_AUTOTUNE_GPUS``) caps the number of GPUs
     used; the default is every visible GPU.  With one GPU the shard runs in this process.
@@ -296,6 +302,12 @@ def run_pipeline(
 
         opts = {"seed": seed, "warmup": warmup, "iters": iters, "detailed": collect_detailed_profile}
         hw_results: list[ProfileResult] = []
+        if shard is not None:
+            rank, world = shard
+            accepted = accepted[rank::world]
+            if rank != 0:
+                compile_errors = []
+            n_use = 1
         if accepted:
             if n_use <= 1:
                 gpu_shard_worker(accepted, opts, hw_results.append)
