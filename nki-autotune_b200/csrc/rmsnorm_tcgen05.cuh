@@ -1,0 +1,234 @@
+// Fused RMSNorm + matmul for sm_100a:  out[M,N] = (x / rms(x) * gamma)[M,K] . w[K,N]
+//
+// Replaces rmsnorm_matmul_online (kernel_library/rmsnorm_matmul/kernel_hand_online.py:198-353).
+// The per-row factor commutes out of the K sum, so the kernel makes ONE pass over x:
+//     out[m,:] = rinv[m] * sum_k (x[m,k] * gamma[k]) * w[k,:],   rinv[m] = rsqrt(mean_k x[m,k]^2 + eps)
+// and the running rescale of the reference's online algorithm (:127-136, :165-192) is not needed
+// because the whole K reduction stays in fp32 tensor memory.
+//
+// Data flow per k-block:
+//   TMA    : x tile [rows x tile_k] (K-major) and w tile [tile_k x cols] (MN-major) -> shared memory
+//   8 transform warps: read the x tile from shared memory (each thread owns one row, half of the
+//            k range), accumulate the row's sum of squares with fp32 FMAs, multiply by gamma
+//            (bf16x2 multiply = one rounding, same as fp32 multiply + round), and write the
+//            scaled tile into a ring of TENSOR-MEMORY slots with tcgen05.st
+//   UMMA   : D[tmem] += A[tmem slot] . B[smem desc]   (A from tensor memory, so the scaled tile
+//            never goes back through shared memory and the MMA's shared-memory reads are w only)
+//   epilogue warps: tcgen05.ld, multiply row m by rinv[m], bf16, global stores
+//
+// Barriers (all waits bounded, see bounded_wait in gemm_tcgen05.cuh):
+//   full_a[s]  x tile landed (local)          empty_a[s] transform warps done reading it (local)
+//   full_b[s]  w tile landed (pair leader)    empty_b[s] UMMAs reading it finished
+//   a_ready[t] slot t written (pair leader)   a_free[t]  UMMAs reading slot t finished
+//   acc_full/acc_empty[b], ss_full/ss_empty[b] as in the plain GEMM
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace b200 {
+
+constexpr int MAX_A_SLOTS = 8;
+constexpr int RMS_TRANSFORM_WARPS = 8;
+constexpr int RMS_THREADS = 32 * (6 + RMS_TRANSFORM_WARPS);
+
+struct RmsParams {
+  int M, N, K;
+  int tile_n, tile_k, stages;
+  int num_m_tiles, num_n_tiles, num_k_blocks;
+  int group_m;
+  int acc_bufs;
+  int tmem_cols;
+  int a_col0;     // first tensor-memory column of the A ring
+  int a_slots;    // ring depth
+  int gamma_bytes;  // bytes of gamma staged in shared memory (0 when gamma is NULL)
+  long long ld_out;
+  float eps, inv_k;
+  __nv_bfloat16* out;
+  const __nv_bfloat16* gamma;
+  int* status;
+  long long timeout_cycles;
+};
+
+struct alignas(16) RmsCtrl {
+  uint64_t full_a[MAX_STAGES];
+  uint64_t full_b[MAX_STAGES];
+  uint64_t empty_a[MAX_STAGES];
+  uint64_t empty_b[MAX_STAGES];
+  uint64_t a_ready[MAX_A_SLOTS];
+  uint64_t a_free[MAX_A_SLOTS];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t ss_full[2];
+  uint64_t ss_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  float ss[2][2][256];  // [accumulator buffer][k half][row]: partial sums of squares
+};
+
+// bounded_wait works on any control block with an abort_flag: thin adapter
+struct RmsWait {
+  RmsCtrl* ctrl;
+  int* status;
+  long long limit;
+  int role;
+};
+
+template <bool CLUSTER_SCOPE>
+__device__ __forceinline__ bool rms_wait(const RmsWait& w, uint32_t bar, uint32_t parity, int bar_id,
+                                         int tile, int kb) {
+  auto try_once = [&]() {
+    if constexpr (CLUSTER_SCOPE) return mbar_try_wait_cluster(bar, parity);
+    else return mbar_try_wait(bar, parity);
+  };
+  if (try_once()) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!try_once()) {
+    if ((++spins & 63u) == 0u) {
+      if (w.ctrl->abort_flag) return false;
+      if (clock64() - t0 > w.limit) {
+        w.ctrl->abort_flag = 1;
+        if (w.status != nullptr && atomicCAS(w.status, 0, 7) == 0) {
+          w.status[1] = w.role;
+          w.status[2] = bar_id;
+          w.status[3] = tile;
+          w.status[4] = kb;
+          w.status[5] = static_cast<int>(blockIdx.x);
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <int CTA_GROUP, int M_SUB>
+__global__ void __launch_bounds__(RMS_THREADS, 1)
+rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
+                       const __grid_constant__ CUtensorMap tm_w, const RmsParams p) {
+  constexpr bool PAIR = (CTA_GROUP == 2);
+  constexpr int MC = 128 * M_SUB;
+  extern __shared__ uint8_t smem_raw[];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+
+  const int tile_n = p.tile_n;
+  const int tile_k = p.tile_k;
+  const int stages = p.stages;
+  const int a_slots = p.a_slots;
+  const int nc = tile_n / CTA_GROUP;
+  const uint32_t a_bytes = static_cast<uint32_t>(MC) * tile_k * 2u;
+  const uint32_t b_bytes = static_cast<uint32_t>(nc) * tile_k * 2u;
+  const int slot_cols = M_SUB * (tile_k / 2);  // tensor-memory columns of one A slot
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_base = smem_base;
+  const uint32_t b_base = a_base + stages * a_bytes;
+  const uint32_t gamma_addr = b_base + stages * b_bytes;
+  const uint32_t ctrl_addr = gamma_addr + ((static_cast<uint32_t>(p.gamma_bytes) + 15u) & ~15u);
+  uint8_t* const smem_gen = smem_raw - smem_u32(smem_raw);  // generic pointer for shared address 0
+  RmsCtrl* ctrl = reinterpret_cast<RmsCtrl*>(smem_gen + ctrl_addr);
+
+  const int acc_cols = M_SUB * tile_n;
+  const int acc_bufs = p.acc_bufs;
+  const int num_k_blocks = p.num_k_blocks;
+  const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int first_tile = static_cast<int>(blockIdx.x) / CTA_GROUP;
+  const int tile_stride = static_cast<int>(gridDim.x) / CTA_GROUP;
+
+  // ------------------------------------------------------------------ set-up
+  if (threadIdx.x == 0) {
+    ctrl->abort_flag = 0;
+    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_w);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full_a[s]), 1);
+      mbar_init(smem_u32(&ctrl->full_b[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty_a[s]), RMS_TRANSFORM_WARPS);
+      mbar_init(smem_u32(&ctrl->empty_b[s]), 1);
+    }
+    for (int t = 0; t < a_slots; ++t) {
+      mbar_init(smem_u32(&ctrl->a_ready[t]), RMS_TRANSFORM_WARPS * CTA_GROUP);
+      mbar_init(smem_u32(&ctrl->a_free[t]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
+      mbar_init(smem_u32(&ctrl->acc_empty[b]), 4 * CTA_GROUP);
+      mbar_init(smem_u32(&ctrl->ss_full[b]), RMS_TRANSFORM_WARPS);
+      mbar_init(smem_u32(&ctrl->ss_empty[b]), 4);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<CTA_GROUP>(smem_u32(&ctrl->tmem_base), static_cast<uint32_t>(p.tmem_cols));
+    tmem_relinquish<CTA_GROUP>();
+  }
+  // gamma -> shared memory (read by every transform warp for every tile)
+  if (p.gamma_bytes > 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.gamma);
+    uint4* dst = reinterpret_cast<uint4*>(smem_gen + gamma_addr);
+    for (int i = threadIdx.x; i < p.gamma_bytes / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (PAIR) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  RmsWait wctx{ctrl, p.status, p.timeout_cycles, 0};
+
+  // ------------------------------------------------------------------ TMA producer
+  if (warp == 0) {
+    if (lane == 0) {
+      wctx.role = ROLE_PRODUCER;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
+        int mt, nt;
+        tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+        const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
+        const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc;
+        for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
+          const int s = it % stages;
+          const uint32_t ph = (it / stages) & 1u;
+          ok = rms_wait<PAIR>(wctx, smem_u32(&ctrl->empty_b[s]), ph ^ 1u, 100 + s, tile, kb);
+          if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ph ^ 1u, 120 + s, tile, kb);
+          if (!ok) break;
+          const uint32_t a_s = a_base + s * a_bytes;
+          const uint32_t b_s = b_base + s * b_bytes;
+          const int k0 = kb * tile_k;
+          const uint32_t fa = smem_u32(&ctrl->full_a[s]);
+          const uint32_t fb = smem_u32(&ctrl->full_b[s]);
+          mbar_arrive_expect_tx(fa, a_bytes);
+          for (int c = 0; c < tile_k / 64; ++c)
+            tma_load_2d(a_s + c * MC * 128, &tm_x, fa, k0 + 64 * c, m_base);
+          if constexpr (PAIR) {
+            const uint32_t fb_leader = map_to_cta(fb, 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(fb, 2u * b_bytes);
+            for (int c = 0; c < nc / 64; ++c)
+              tma_load_2d_pair(b_s + c * tile_k * 128, &tm_w, fb_leader, n_base + 64 * c, k0);
+          } else {
+            mbar_arrive_expect_tx(fb, b_bytes);
+            for (int c = 0; c < nc / 64; ++c)
+              tma_load_2d(b_s + c * tile_k * 128, &tm_w, fb, n_base + 64 * c, k0);
+          }
+        }
+      }
+      for (int i = 0; i < stages && ok; ++i, ++it) {  // tail: all stages released
+        const int s = it % stages;
+        const uint32_t ph = (it / stages) & 1u;
+        ok = rms_wait<PAIR>(wctx, smem_u32(&ctrl->empty_b[s]), ph ^ 1u, 150 + s, -1, i);
+        if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ph ^ 1u, 170 + s, -1, i);
+      }
+    }
+    __syncwarp();
+  }
