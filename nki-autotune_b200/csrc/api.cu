@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "gemm_tcgen05.cuh"
+#include "rmsnorm_tcgen05.cuh"
 #include "host_api.h"
 
 namespace b200 {
@@ -49,6 +50,8 @@ struct Plan {
   int cluster;     // launch cluster size
   int tile_m, tile_n, tile_k, stages, group_m;
   int acc_bufs, tmem_cols;
+  int a_col0, a_slots;  // fused kernel: tensor-memory ring that holds the scaled x tiles
+  long gamma_bytes;     // fused kernel: shared memory reserved for gamma
   long smem_bytes;
 };
 
@@ -108,18 +111,37 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
   p.group_m = cfg.swizzle > 0 ? cfg.swizzle : (p.cta_group == 2 || p.m_sub == 2 ? 8 : 16);
 
   const int acc_cols = p.m_sub * p.tile_n;
-  p.acc_bufs = (2 * acc_cols <= 512) ? 2 : 1;
-  p.tmem_cols = next_pow2_cols(acc_cols * p.acc_bufs);
   const long mc = 128L * p.m_sub;
   const long stage_bytes = (mc + nc) * p.tile_k * 2L;
-  p.smem_bytes = 1024 + p.stages * stage_bytes + static_cast<long>(sizeof(Ctrl));
+  long ctrl_bytes = static_cast<long>(sizeof(Ctrl));
+  int tmem_need = acc_cols;
+  if (fam == FAM_RMSNORM) {
+    // accumulators first, then as many x-tile slots as fit (at least 2); prefer two accumulator
+    // buffers when that still leaves 2 slots
+    const int slot_cols = p.m_sub * (p.tile_k / 2);
+    p.acc_bufs = (2 * acc_cols + 2 * slot_cols <= 512) ? 2 : 1;
+    p.a_col0 = acc_cols * p.acc_bufs;
+    int slots = (512 - p.a_col0) / slot_cols;
+    if (slots > MAX_A_SLOTS) slots = MAX_A_SLOTS;
+    if (slots > p.stages && p.stages >= 2) slots = p.stages;
+    p.a_slots = slots;
+    tmem_need = p.a_col0 + 2 * slot_cols;
+    p.tmem_cols = next_pow2_cols(p.a_col0 + (slots > 0 ? slots : 2) * slot_cols);
+    p.gamma_bytes = ((K > 0 ? K : 0) * 2L + 15) & ~15L;
+    ctrl_bytes = static_cast<long>(sizeof(RmsCtrl)) + p.gamma_bytes;
+  } else {
+    p.acc_bufs = (2 * acc_cols <= 512) ? 2 : 1;
+    p.tmem_cols = next_pow2_cols(acc_cols * p.acc_bufs);
+  }
+  p.smem_bytes = 1024 + p.stages * stage_bytes + ctrl_bytes;
   *plan = p;
-  if (acc_cols > 512)
-    return set_error(B200_ERR_TMEM_OOM, "Out of memory in tmem: accumulator needs %d of 512 columns", acc_cols);
+  if (tmem_need > 512)
+    return set_error(B200_ERR_TMEM_OOM, "Out of memory in tmem: accumulator%s need %d of 512 columns",
+                     fam == FAM_RMSNORM ? " and two x-tile slots" : "", tmem_need);
   if (p.smem_bytes > SMEM_BUDGET)
     return set_error(B200_ERR_SMEM_OOM,
                      "Out of memory in smem: %d stages x %ld B + %ld B control = %ld B > %ld B per CTA",
-                     p.stages, stage_bytes, 1024 + static_cast<long>(sizeof(Ctrl)), p.smem_bytes, SMEM_BUDGET);
+                     p.stages, stage_bytes, 1024 + ctrl_bytes, p.smem_bytes, SMEM_BUDGET);
   if (M != 0 || N != 0 || K != 0) {
     if (M <= 0 || N <= 0 || K <= 0) return set_error(B200_ERR_BAD_SHAPE, "empty shape M=%ld N=%ld K=%ld", M, N, K);
     if (M % 8 != 0 || N % 8 != 0)
@@ -172,16 +194,18 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long rows, long col
 
 // ---------------------------------------------------------------------------- launch
 typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+typedef void (*RmsKernelFn)(const CUtensorMap, const CUtensorMap, const RmsParams);
 
-static GemmKernelFn pick_kernel(Family fam, const Plan& p) {
-  if (fam == FAM_LHST) {
-    if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, MODE_LHST>;
-    if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, MODE_LHST>;
-    return gemm_tcgen05_kernel<1, 1, MODE_LHST>;
-  }
-  if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, MODE_RMSNORM>;
-  if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, MODE_RMSNORM>;
-  return gemm_tcgen05_kernel<1, 1, MODE_RMSNORM>;
+static GemmKernelFn pick_gemm_kernel(const Plan& p) {
+  if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1>;
+  if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2>;
+  return gemm_tcgen05_kernel<1, 1>;
+}
+
+static RmsKernelFn pick_rms_kernel(const Plan& p) {
+  if (p.cta_group == 2) return rmsnorm_tcgen05_kernel<2, 1>;
+  if (p.m_sub == 2) return rmsnorm_tcgen05_kernel<1, 2>;
+  return rmsnorm_tcgen05_kernel<1, 1>;
 }
 
 struct DeviceInfo {
@@ -222,9 +246,12 @@ struct LaunchArgs {
 
 // A prepared launch: tensor maps and parameters are built once and can be replayed.
 struct Prepared {
-  GemmKernelFn fn;
+  GemmKernelFn fn;      // plain GEMM (fam == FAM_LHST)
+  RmsKernelFn rms_fn;   // fused kernel (fam == FAM_RMSNORM)
   CUtensorMap tm_a, tm_b;
   GemmParams gp;
+  RmsParams rp;
+  bool fused;
   Plan plan;
   dim3 grid, block;
   size_t smem;
@@ -268,22 +295,45 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   gp.acc_bufs = plan.acc_bufs;
   gp.tmem_cols = plan.tmem_cols;
   gp.ld_out = la.ld_out;
-  gp.eps = la.eps;
-  gp.inv_k = 1.0f / static_cast<float>(la.K);
   gp.out = static_cast<__nv_bfloat16*>(la.out);
-  gp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
   gp.status = dev_status;
   long long limit_us = 1000000;  // one second per wait
   if (cfg && cfg->reserved[1] > 0) limit_us = cfg->reserved[1];
   gp.timeout_cycles = limit_us * (di.clock_khz > 0 ? di.clock_khz / 1000 : 1900);
-  gp.debug_skip_producer = (cfg && cfg->reserved[0] == 1) ? 1 : 0;
+  gp.debug_mode = cfg ? cfg->reserved[0] : 0;
 
-  pr->fn = pick_kernel(la.fam, plan);
+  const bool fused = (la.fam == FAM_RMSNORM);
+  RmsParams& rp = pr->rp;
+  memset(&rp, 0, sizeof(rp));
+  if (fused) {
+    if (plan.a_slots < 2)
+      return set_error(B200_ERR_TMEM_OOM, "Out of memory in tmem: fewer than two x-tile slots fit beside the accumulators");
+    rp.M = gp.M; rp.N = gp.N; rp.K = gp.K;
+    rp.tile_n = gp.tile_n; rp.tile_k = gp.tile_k; rp.stages = gp.stages;
+    rp.num_m_tiles = gp.num_m_tiles; rp.num_n_tiles = gp.num_n_tiles; rp.num_k_blocks = gp.num_k_blocks;
+    rp.group_m = gp.group_m;
+    rp.acc_bufs = plan.acc_bufs;
+    rp.tmem_cols = plan.tmem_cols;
+    rp.a_col0 = plan.a_col0;
+    rp.a_slots = plan.a_slots;
+    rp.gamma_bytes = la.gamma ? static_cast<int>(plan.gamma_bytes) : 0;
+    rp.ld_out = gp.ld_out;
+    rp.eps = la.eps;
+    rp.inv_k = 1.0f / static_cast<float>(la.K);
+    rp.out = gp.out;
+    rp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
+    rp.status = gp.status;
+    rp.timeout_cycles = gp.timeout_cycles;
+  }
+  pr->fn = pick_gemm_kernel(plan);
+  pr->rms_fn = pick_rms_kernel(plan);
+  pr->fused = fused;
   pr->plan = plan;
   pr->smem = static_cast<size_t>(plan.smem_bytes);
-  pr->block = dim3(static_cast<unsigned>(gemm_threads(la.fam == FAM_RMSNORM ? MODE_RMSNORM : MODE_LHST)));
-  rc = check_cuda(cudaFuncSetAttribute(reinterpret_cast<const void*>(pr->fn),
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pr->smem)),
+  pr->block = dim3(static_cast<unsigned>(fused ? RMS_THREADS : GEMM_THREADS));
+  const void* kernel_ptr = fused ? reinterpret_cast<const void*>(pr->rms_fn) : reinterpret_cast<const void*>(pr->fn);
+  rc = check_cuda(cudaFuncSetAttribute(kernel_ptr, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(pr->smem)),
                   "cudaFuncSetAttribute(max dynamic shared memory)");
   if (rc) return rc;
 
@@ -303,7 +353,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
     qc.attrs = qa;
     qc.numAttrs = 1;
     int max_clusters = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, reinterpret_cast<const void*>(pr->fn), &qc);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel_ptr, &qc);
     if (e == cudaSuccess && max_clusters > 0 && max_clusters < groups) groups = max_clusters;
     (void)cudaGetLastError();
   }
@@ -329,6 +379,8 @@ static int launch(const Prepared& pr, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
+  if (pr.fused)
+    return check_cuda(cudaLaunchKernelEx(&lc, pr.rms_fn, pr.tm_a, pr.tm_b, pr.rp), "fused RMSNorm GEMM launch");
   return check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.gp), "tcgen05 GEMM launch");
 }
 

@@ -8,8 +8,8 @@
 //
 // Data flow per k-block:
 //   TMA    : x tile [rows x tile_k] (K-major) and w tile [tile_k x cols] (MN-major) -> shared memory
-//   8 transform warps: read the x tile from shared memory (each thread owns one row, half of the
-//            k range), accumulate the row's sum of squares with fp32 FMAs, multiply by gamma
+//   8 transform warps (two groups of four taking alternate k-blocks, so two tiles are in
+//            flight): read the x tile from shared memory (each thread owns one row), accumulate the row's sum of squares with fp32 FMAs, multiply by gamma
 //            (bf16x2 multiply = one rounding, same as fp32 multiply + round), and write the
 //            scaled tile into a ring of TENSOR-MEMORY slots with tcgen05.st
 //   UMMA   : D[tmem] += A[tmem slot] . B[smem desc]   (A from tensor memory, so the scaled tile
@@ -61,7 +61,7 @@ struct alignas(16) RmsCtrl {
   uint64_t ss_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
-  float ss[2][2][256];  // [accumulator buffer][k half][row]: partial sums of squares
+  float ss[2][2][256];  // [accumulator buffer][warp group][row]: partial sums of squares
 };
 
 // bounded_wait works on any control block with an abort_flag: thin adapter
@@ -150,11 +150,11 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
     for (int s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&ctrl->full_a[s]), 1);
       mbar_init(smem_u32(&ctrl->full_b[s]), 1);
-      mbar_init(smem_u32(&ctrl->empty_a[s]), RMS_TRANSFORM_WARPS);
+      mbar_init(smem_u32(&ctrl->empty_a[s]), RMS_TRANSFORM_WARPS / 2);
       mbar_init(smem_u32(&ctrl->empty_b[s]), 1);
     }
     for (int t = 0; t < a_slots; ++t) {
-      mbar_init(smem_u32(&ctrl->a_ready[t]), RMS_TRANSFORM_WARPS * CTA_GROUP);
+      mbar_init(smem_u32(&ctrl->a_ready[t]), (RMS_TRANSFORM_WARPS / 2) * CTA_GROUP);
       mbar_init(smem_u32(&ctrl->a_free[t]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -190,17 +190,17 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
   if (warp == 0) {
     if (lane == 0) {
       wctx.role = ROLE_PRODUCER;
-      uint32_t it = 0;
+      Ring ring;
       bool ok = true;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
         int mt, nt;
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
         const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc;
-        for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-          const int s = it % stages;
-          const uint32_t ph = (it / stages) & 1u;
-          ok = rms_wait<PAIR>(wctx, smem_u32(&ctrl->empty_b[s]), ph ^ 1u, 100 + s, tile, kb);
+        for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(stages)) {
+          const uint32_t s = ring.s;
+          const uint32_t ph = ring.ph;
+          ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[s]), ph ^ 1u, 100 + s, tile, kb);
           if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ph ^ 1u, 120 + s, tile, kb);
           if (!ok) break;
           const uint32_t a_s = a_base + s * a_bytes;
@@ -223,12 +223,228 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
           }
         }
       }
-      for (int i = 0; i < stages && ok; ++i, ++it) {  // tail: all stages released
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1u;
-        ok = rms_wait<PAIR>(wctx, smem_u32(&ctrl->empty_b[s]), ph ^ 1u, 150 + s, -1, i);
-        if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ph ^ 1u, 170 + s, -1, i);
+      for (int i = 0; i < stages && ok; ++i, ring.advance(stages)) {  // tail: all stages released
+        ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1, i);
+        if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[ring.s]), ring.ph ^ 1u, 170 + ring.s, -1, i);
       }
     }
     __syncwarp();
   }
+  // ------------------------------------------------------------------ UMMA issuer
+  else if (warp == 1) {
+    if (lane == 0 && cta_rank == 0) {
+      wctx.role = ROLE_MMA;
+      const uint32_t idesc = make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, 0, 1);
+      const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
+      const uint64_t b_desc0 = make_smem_desc_sw128(b_base, mn_lbo, 1024);
+      const uint32_t b_step = b_bytes >> 4;
+      const int nk16 = tile_k / 16;
+      Ring ring, slot, acc;
+      bool ok = true;
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
+        const uint32_t b = acc.s;
+        ok = rms_wait<false>(wctx, smem_u32(&ctrl->acc_empty[b]), acc.ph ^ 1u, 200 + b, tile, -1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + b * static_cast<uint32_t>(acc_cols);
+        for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(stages), slot.advance(a_slots)) {
+          const uint32_t s = ring.s;
+          const uint32_t ta = slot.s;
+          ok = rms_wait<false>(wctx, smem_u32(&ctrl->full_b[s]), ring.ph, 300 + s, tile, kb);
+          if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->a_ready[ta]), slot.ph, 400 + ta, tile, kb);
+          if (!ok) break;
+          tc_fence_after();
+          uint64_t bdesc = b_desc0 + s * b_step;
+          uint32_t a_tmem = tmem_base + static_cast<uint32_t>(p.a_col0) + ta * static_cast<uint32_t>(slot_cols);
+#pragma unroll 4
+          for (int k16 = 0; k16 < nk16; ++k16, bdesc += 128, a_tmem += 8) {
+#pragma unroll
+            for (int mi = 0; mi < M_SUB; ++mi)
+              umma_bf16_ts<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n),
+                                      a_tmem + static_cast<uint32_t>(mi * (tile_k / 2)), bdesc, idesc,
+                                      (kb | k16) != 0 ? 1u : 0u);
+          }
+          if constexpr (PAIR) {
+            umma_commit_pair(smem_u32(&ctrl->empty_b[s]), 3);
+            umma_commit_pair(smem_u32(&ctrl->a_free[ta]), 3);
+          } else {
+            umma_commit_1cta(smem_u32(&ctrl->empty_b[s]));
+            umma_commit_1cta(smem_u32(&ctrl->a_free[ta]));
+          }
+        }
+        if (!ok) break;
+        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->acc_full[b]), 3);
+        else umma_commit_1cta(smem_u32(&ctrl->acc_full[b]));
+      }
+    }
+    __syncwarp();
+  }
+  // ------------------------------------------------------------------ epilogue
+  else if (warp < 6) {
+    wctx.role = ROLE_EPILOGUE;
+    const int q = warp & 3;
+    const int row_in_cta = q * 32 + lane;
+    const uint32_t acc_empty_leader =
+        PAIR ? map_to_cta(smem_u32(&ctrl->acc_empty[0]), 0) : smem_u32(&ctrl->acc_empty[0]);
+    Ring acc;
+    bool ok = true;
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
+      int mt, nt;
+      tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+      const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
+      const int n_base = nt * tile_n;
+      const int b = static_cast<int>(acc.s);
+      const uint32_t aph = acc.ph;
+      ok = rms_wait<false>(wctx, smem_u32(&ctrl->acc_full[b]), aph, 500 + b, tile, -1);
+      if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->ss_full[b]), aph, 600 + b, tile, -1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int mi = 0; mi < M_SUB; ++mi) {
+        const int r = mi * 128 + row_in_cta;
+        const long long grow = static_cast<long long>(m_base) + r;
+        const float scale = rsqrtf((ctrl->ss[b][0][r] + ctrl->ss[b][1][r]) * p.inv_k + p.eps);
+        __nv_bfloat16* out_row = p.out + grow * p.ld_out;
+        for (int c = 0; c < tile_n / 32; ++c) {
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                 static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 32);
+          tmem_ld_32x32b_x32(taddr, v);
+          tmem_ld_wait();
+          if (grow < p.M) {
+            const int col0 = n_base + c * 32;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + g * 8;
+              if (col + 8 <= p.N) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * scale, __uint_as_float(v[g * 8 + 1]) * scale);
+                o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * scale, __uint_as_float(v[g * 8 + 3]) * scale);
+                o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * scale, __uint_as_float(v[g * 8 + 5]) * scale);
+                o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * scale, __uint_as_float(v[g * 8 + 7]) * scale);
+                *reinterpret_cast<uint4*>(out_row + col) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(acc_empty_leader + b * 8);
+        else mbar_arrive(acc_empty_leader + b * 8);
+        mbar_arrive(smem_u32(&ctrl->ss_empty[b]));
+      }
+    }
+  }
+  // ------------------------------------------------------------------ transform warps
+  else {
+    wctx.role = ROLE_TRANSFORM;
+    const int q = warp & 3;                 // tensor-memory lane quadrant of this warp
+    const int group = (warp - 6) >> 2;      // two groups of four warps take alternate k-blocks
+    const int row = q * 32 + lane;          // row within a 128-row block
+    const uint32_t sw = static_cast<uint32_t>(row & 7);
+    const bool has_gamma = p.gamma_bytes > 0;
+    const uint8_t* gamma_s = smem_gen + gamma_addr;
+    const uint32_t a_ready_leader_base =
+        PAIR ? map_to_cta(smem_u32(&ctrl->a_ready[0]), 0) : smem_u32(&ctrl->a_ready[0]);
+    uint32_t it = 0;
+    Ring ring, slot, acc;
+    bool ok = true;
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
+      float ss[M_SUB];
+#pragma unroll
+      for (int mi = 0; mi < M_SUB; ++mi) ss[mi] = 0.0f;
+      for (int kb = 0; kb < num_k_blocks; ++kb, ++it, ring.advance(stages), slot.advance(a_slots)) {
+        if (static_cast<int>(it & 1u) != group) continue;  // the other group's k-block
+        const uint32_t s = ring.s;
+        const uint32_t ph = ring.ph;
+        const uint32_t ta = slot.s;
+        const uint32_t tph = slot.ph;
+        ok = rms_wait<false>(wctx, smem_u32(&ctrl->full_a[s]), ph, 700 + s, tile, kb);
+        if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->a_free[ta]), tph ^ 1u, 720 + ta, tile, kb);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint8_t* a_s = smem_gen + a_base + s * a_bytes;
+        const int k0 = kb * tile_k;
+        for (int grp = 0; grp < tile_k / 32; ++grp) {
+          const int e0 = grp * 32;        // first k element (within the stage) of this group of 32
+          const int chunk = e0 >> 6;      // 64-wide shared-memory chunk
+          const int j0 = (e0 & 63) >> 3;  // first 16-byte piece within the row
+          const uint4* g4 = reinterpret_cast<const uint4*>(gamma_s + (k0 + e0) * 2);
+#pragma unroll
+          for (int mi = 0; mi < M_SUB; ++mi) {
+            const uint8_t* rowp = a_s + chunk * (MC * 128) + (mi * 128 + row) * 128;
+            uint32_t r[16];
+            float acc = ss[mi];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((static_cast<uint32_t>(j0 + jj) ^ sw) << 4));
+              const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+              uint32_t g[4] = {0, 0, 0, 0};
+              if (has_gamma) {
+                const uint4 gv = g4[jj];
+                g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+              }
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const float lo = __uint_as_float(w4[w] << 16);
+                const float hi = __uint_as_float(w4[w] & 0xffff0000u);
+                acc = fmaf(lo, lo, acc);
+                acc = fmaf(hi, hi, acc);
+                r[jj * 4 + w] = has_gamma ? mul_bf16x2(w4[w], g[w]) : w4[w];
+              }
+            }
+            ss[mi] = acc;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                   static_cast<uint32_t>(p.a_col0 + ta * slot_cols + mi * (tile_k / 2) + (e0 >> 1));
+            tmem_st_32x32b_x16(taddr, r);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&ctrl->empty_a[s]));
+          if constexpr (PAIR) mbar_arrive_cluster(a_ready_leader_base + ta * 8);
+          else mbar_arrive(a_ready_leader_base + ta * 8);
+        }
+      }
+      if (!ok) break;
+      const int b = static_cast<int>(acc.s);
+      const uint32_t aph = acc.ph;
+      ok = rms_wait<false>(wctx, smem_u32(&ctrl->ss_empty[b]), aph ^ 1u, 800 + b, tile, -1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll
+      for (int mi = 0; mi < M_SUB; ++mi) ctrl->ss[b][group][mi * 128 + row] = ss[mi];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->ss_full[b]));
+    }
+    // tail: every slot released, so no UMMA-completion arrival is still on its way to a_free[]
+    for (int i = 0; i < a_slots && ok; ++i, slot.advance(a_slots)) {
+      ok = rms_wait<false>(wctx, smem_u32(&ctrl->a_free[slot.s]), slot.ph ^ 1u, 750 + slot.s, -1, i);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (ctrl->abort_flag && threadIdx.x == 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) __nanosleep(1000);
+  }
+  if constexpr (PAIR) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<CTA_GROUP>(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+}
+
+}  // namespace b200
