@@ -51,6 +51,7 @@ struct Plan {
   int tile_m, tile_n, tile_k, stages, group_m;
   int acc_bufs, tmem_cols;
   int a_col0, a_slots;  // fused kernel: tensor-memory ring that holds the scaled x tiles
+  int a_stages, groups; // fused kernel: shared-memory ring of x tiles; transform warp groups
   long gamma_bytes;     // fused kernel: shared memory reserved for gamma
   long smem_bytes;
 };
@@ -123,17 +124,30 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     p.a_col0 = acc_cols * p.acc_bufs;
     int slots = (512 - p.a_col0) / slot_cols;
     if (slots > MAX_A_SLOTS) slots = MAX_A_SLOTS;
-    if (slots > p.stages && p.stages >= 2) slots = p.stages;
-    p.a_slots = slots;
     tmem_need = p.a_col0 + 2 * slot_cols;
-    p.tmem_cols = next_pow2_cols(p.a_col0 + (slots > 0 ? slots : 2) * slot_cols);
     p.gamma_bytes = ((K > 0 ? K : 0) * 2L + 15) & ~15L;
     ctrl_bytes = static_cast<long>(sizeof(RmsCtrl)) + p.gamma_bytes;
+    // x ring: as deep as fits beside the w ring (8, 6, 4, 3, 2 or 1 stages).  The transform warp
+    // groups take k-blocks round-robin, and both the x ring and the slot ring must be multiples
+    // of the group count (a stage/slot is then always served by one group, in order).
+    const long a_stage_bytes = mc * p.tile_k * 2L;
+    const long b_stage_bytes = static_cast<long>(nc) * p.tile_k * 2L;
+    static const int kDepths[6] = {8, 6, 4, 3, 2, 1};
+    p.a_stages = 1;
+    for (int d : kDepths)
+      if (1024 + p.stages * b_stage_bytes + d * a_stage_bytes + ctrl_bytes <= SMEM_BUDGET) { p.a_stages = d; break; }
+    p.groups = 1;
+    for (int g = 4; g >= 1; --g)
+      if (p.a_stages % g == 0 && slots >= g) { p.groups = g; break; }
+    slots -= slots % p.groups;
+    p.a_slots = slots;
+    p.tmem_cols = next_pow2_cols(p.a_col0 + (slots > 0 ? slots : 2) * slot_cols);
+    p.smem_bytes = 1024 + p.stages * b_stage_bytes + p.a_stages * a_stage_bytes + ctrl_bytes;
   } else {
     p.acc_bufs = (2 * acc_cols <= 512) ? 2 : 1;
     p.tmem_cols = next_pow2_cols(acc_cols * p.acc_bufs);
   }
-  p.smem_bytes = 1024 + p.stages * stage_bytes + ctrl_bytes;
+  if (fam != FAM_RMSNORM) p.smem_bytes = 1024 + p.stages * stage_bytes + ctrl_bytes;
   *plan = p;
   if (tmem_need > 512)
     return set_error(B200_ERR_TMEM_OOM, "Out of memory in tmem: accumulator%s need %d of 512 columns",
@@ -316,6 +330,8 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
     rp.tmem_cols = plan.tmem_cols;
     rp.a_col0 = plan.a_col0;
     rp.a_slots = plan.a_slots;
+    rp.a_stages = plan.a_stages;
+    rp.groups = plan.groups;
     rp.gamma_bytes = la.gamma ? static_cast<int>(plan.gamma_bytes) : 0;
     rp.ld_out = gp.ld_out;
     rp.eps = la.eps;
@@ -324,6 +340,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
     rp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
     rp.status = gp.status;
     rp.timeout_cycles = gp.timeout_cycles;
+    rp.debug_mode = gp.debug_mode;
   }
   pr->fn = pick_gemm_kernel(plan);
   pr->rms_fn = pick_rms_kernel(plan);

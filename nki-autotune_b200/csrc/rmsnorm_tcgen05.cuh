@@ -8,8 +8,8 @@
 //
 // Data flow per k-block:
 //   TMA    : x tile [rows x tile_k] (K-major) and w tile [tile_k x cols] (MN-major) -> shared memory
-//   8 transform warps (two groups of four taking alternate k-blocks, so two tiles are in
-//            flight): read the x tile from shared memory (each thread owns one row), accumulate the row's sum of squares with fp32 FMAs, multiply by gamma
+//   16 transform warps (four groups of four taking k-blocks round-robin, so four x tiles
+//            are in flight): read the x tile from shared memory (each thread owns one row), accumulate the row's sum of squares with fp32 FMAs, multiply by gamma
 //            (bf16x2 multiply = one rounding, same as fp32 multiply + round), and write the
 //            scaled tile into a ring of TENSOR-MEMORY slots with tcgen05.st
 //   UMMA   : D[tmem] += A[tmem slot] . B[smem desc]   (A from tensor memory, so the scaled tile
@@ -27,8 +27,10 @@
 namespace b200 {
 
 constexpr int MAX_A_SLOTS = 8;
-constexpr int RMS_TRANSFORM_WARPS = 8;
-constexpr int RMS_THREADS = 32 * (6 + RMS_TRANSFORM_WARPS);
+constexpr int RMS_TRANSFORM_GROUPS = 4;  // groups of four warps (one per tensor-memory lane quadrant)
+constexpr int RMS_TRANSFORM_WARPS = 4 * RMS_TRANSFORM_GROUPS;
+constexpr int RMS_A_PRODUCER_WARP = 6 + RMS_TRANSFORM_WARPS;  // last warp
+constexpr int RMS_THREADS = 32 * (7 + RMS_TRANSFORM_WARPS);
 
 struct RmsParams {
   int M, N, K;
@@ -38,7 +40,9 @@ struct RmsParams {
   int acc_bufs;
   int tmem_cols;
   int a_col0;     // first tensor-memory column of the A ring
-  int a_slots;    // ring depth
+  int a_slots;    // ring depth (a multiple of groups)
+  int a_stages;   // depth of the shared-memory ring of x tiles (a multiple of groups)
+  int groups;     // transform warp groups in use: 1, 2 or 4
   int gamma_bytes;  // bytes of gamma staged in shared memory (0 when gamma is NULL)
   long long ld_out;
   float eps, inv_k;
@@ -46,7 +50,10 @@ struct RmsParams {
   const __nv_bfloat16* gamma;
   int* status;
   long long timeout_cycles;
+  int debug_mode;  // 0, DEBUG_NO_MMA, or DEBUG_NO_TRANSFORM (measurement hooks)
 };
+
+constexpr int DEBUG_NO_TRANSFORM = 4;  // transform warps only cycle the barriers
 
 struct alignas(16) RmsCtrl {
   uint64_t full_a[MAX_STAGES];
@@ -61,7 +68,7 @@ struct alignas(16) RmsCtrl {
   uint64_t ss_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
-  float ss[2][2][256];  // [accumulator buffer][warp group][row]: partial sums of squares
+  float ss[2][RMS_TRANSFORM_GROUPS][256];  // [accumulator buffer][warp group][row]: partial sums of squares
 };
 
 // bounded_wait works on any control block with an abort_flag: thin adapter
@@ -122,6 +129,7 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
   const int tile_k = p.tile_k;
   const int stages = p.stages;
   const int a_slots = p.a_slots;
+  const int a_stages = p.a_stages;
   const int nc = tile_n / CTA_GROUP;
   const uint32_t a_bytes = static_cast<uint32_t>(MC) * tile_k * 2u;
   const uint32_t b_bytes = static_cast<uint32_t>(nc) * tile_k * 2u;
@@ -129,7 +137,7 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
-  const uint32_t b_base = a_base + stages * a_bytes;
+  const uint32_t b_base = a_base + a_stages * a_bytes;
   const uint32_t gamma_addr = b_base + stages * b_bytes;
   const uint32_t ctrl_addr = gamma_addr + ((static_cast<uint32_t>(p.gamma_bytes) + 15u) & ~15u);
   uint8_t* const smem_gen = smem_raw - smem_u32(smem_raw);  // generic pointer for shared address 0
@@ -148,19 +156,21 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_w);
     for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&ctrl->full_a[s]), 1);
       mbar_init(smem_u32(&ctrl->full_b[s]), 1);
-      mbar_init(smem_u32(&ctrl->empty_a[s]), RMS_TRANSFORM_WARPS / 2);
       mbar_init(smem_u32(&ctrl->empty_b[s]), 1);
     }
+    for (int s = 0; s < a_stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full_a[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty_a[s]), 4);
+    }
     for (int t = 0; t < a_slots; ++t) {
-      mbar_init(smem_u32(&ctrl->a_ready[t]), (RMS_TRANSFORM_WARPS / 2) * CTA_GROUP);
+      mbar_init(smem_u32(&ctrl->a_ready[t]), 4 * CTA_GROUP);
       mbar_init(smem_u32(&ctrl->a_free[t]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
       mbar_init(smem_u32(&ctrl->acc_empty[b]), 4 * CTA_GROUP);
-      mbar_init(smem_u32(&ctrl->ss_full[b]), RMS_TRANSFORM_WARPS);
+      mbar_init(smem_u32(&ctrl->ss_full[b]), 4 * p.groups);
       mbar_init(smem_u32(&ctrl->ss_empty[b]), 4);
     }
     fence_mbar_init();
@@ -186,7 +196,9 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
 
   RmsWait wctx{ctrl, p.status, p.timeout_cycles, 0};
 
-  // ------------------------------------------------------------------ TMA producer
+  // ------------------------------------------------------------------ TMA producer, w tiles
+  // The x and w rings advance independently (separate producer warps, separate barriers), so
+  // the transform of later x tiles runs ahead while earlier w tiles are still being consumed.
   if (warp == 0) {
     if (lane == 0) {
       wctx.role = ROLE_PRODUCER;
@@ -195,22 +207,14 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
         int mt, nt;
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
-        const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
         const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc;
         for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(stages)) {
           const uint32_t s = ring.s;
-          const uint32_t ph = ring.ph;
-          ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[s]), ph ^ 1u, 100 + s, tile, kb);
-          if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ph ^ 1u, 120 + s, tile, kb);
+          ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[s]), ring.ph ^ 1u, 100 + s, tile, kb);
           if (!ok) break;
-          const uint32_t a_s = a_base + s * a_bytes;
           const uint32_t b_s = b_base + s * b_bytes;
           const int k0 = kb * tile_k;
-          const uint32_t fa = smem_u32(&ctrl->full_a[s]);
           const uint32_t fb = smem_u32(&ctrl->full_b[s]);
-          mbar_arrive_expect_tx(fa, a_bytes);
-          for (int c = 0; c < tile_k / 64; ++c)
-            tma_load_2d(a_s + c * MC * 128, &tm_x, fa, k0 + 64 * c, m_base);
           if constexpr (PAIR) {
             const uint32_t fb_leader = map_to_cta(fb, 0);
             if (cta_rank == 0) mbar_arrive_expect_tx(fb, 2u * b_bytes);
@@ -223,10 +227,35 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
           }
         }
       }
-      for (int i = 0; i < stages && ok; ++i, ring.advance(stages)) {  // tail: all stages released
+      for (int i = 0; i < stages && ok; ++i, ring.advance(stages))  // tail: all stages released
         ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1, i);
-        if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[ring.s]), ring.ph ^ 1u, 170 + ring.s, -1, i);
+    }
+    __syncwarp();
+  }
+  // ------------------------------------------------------------------ TMA producer, x tiles
+  else if (warp == RMS_A_PRODUCER_WARP) {
+    if (lane == 0) {
+      wctx.role = ROLE_PRODUCER;
+      Ring ring;
+      bool ok = true;
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
+        int mt, nt;
+        tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
+        const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
+        for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(a_stages)) {
+          const uint32_t s = ring.s;
+          ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ring.ph ^ 1u, 120 + s, tile, kb);
+          if (!ok) break;
+          const uint32_t a_s = a_base + s * a_bytes;
+          const int k0 = kb * tile_k;
+          const uint32_t fa = smem_u32(&ctrl->full_a[s]);
+          mbar_arrive_expect_tx(fa, a_bytes);
+          for (int c = 0; c < tile_k / 64; ++c)
+            tma_load_2d(a_s + c * MC * 128, &tm_x, fa, k0 + 64 * c, m_base);
+        }
       }
+      for (int i = 0; i < a_stages && ok; ++i, ring.advance(a_stages))
+        ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[ring.s]), ring.ph ^ 1u, 170 + ring.s, -1, i);
     }
     __syncwarp();
   }
@@ -260,7 +289,8 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
           for (int k16 = 0; k16 < nk16; ++k16, bdesc += 128, a_tmem += 8) {
 #pragma unroll
             for (int mi = 0; mi < M_SUB; ++mi)
-              umma_bf16_ts<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n),
+              if (p.debug_mode != DEBUG_NO_MMA)
+                umma_bf16_ts<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n),
                                       a_tmem + static_cast<uint32_t>(mi * (tile_k / 2)), bdesc, idesc,
                                       (kb | k16) != 0 ? 1u : 0u);
           }
@@ -304,7 +334,11 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
       for (int mi = 0; mi < M_SUB; ++mi) {
         const int r = mi * 128 + row_in_cta;
         const long long grow = static_cast<long long>(m_base) + r;
-        const float scale = rsqrtf((ctrl->ss[b][0][r] + ctrl->ss[b][1][r]) * p.inv_k + p.eps);
+        float sumsq = 0.0f;
+#pragma unroll
+        for (int gidx = 0; gidx < RMS_TRANSFORM_GROUPS; ++gidx)
+          if (gidx < p.groups) sumsq += ctrl->ss[b][gidx][r];
+        const float scale = rsqrtf(sumsq * p.inv_k + p.eps);
         __nv_bfloat16* out_row = p.out + grow * p.ld_out;
         for (int c = 0; c < tile_n / 32; ++c) {
           uint32_t v[32];
@@ -342,7 +376,7 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
   else {
     wctx.role = ROLE_TRANSFORM;
     const int q = warp & 3;                 // tensor-memory lane quadrant of this warp
-    const int group = (warp - 6) >> 2;      // two groups of four warps take alternate k-blocks
+    const int group = (warp - 6) >> 2;      // groups of four warps take k-blocks round-robin
     const int row = q * 32 + lane;          // row within a 128-row block
     const uint32_t sw = static_cast<uint32_t>(row & 7);
     const bool has_gamma = p.gamma_bytes > 0;
@@ -352,12 +386,17 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
     uint32_t it = 0;
     Ring ring, slot, acc;
     bool ok = true;
+    const int groups = p.groups;
+    if (group >= groups) ok = false;  // this group is not used by the current configuration
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
       float ss[M_SUB];
 #pragma unroll
       for (int mi = 0; mi < M_SUB; ++mi) ss[mi] = 0.0f;
-      for (int kb = 0; kb < num_k_blocks; ++kb, ++it, ring.advance(stages), slot.advance(a_slots)) {
-        if (static_cast<int>(it & 1u) != group) continue;  // the other group's k-block
+      for (int kb = 0; kb < num_k_blocks; ++kb, ++it, ring.advance(a_stages), slot.advance(a_slots)) {
+        // Round-robin over the groups.  Both ring depths are multiples of `groups`, so a given
+        // stage and a given slot are always served by the same group, in order: a group never
+        // waits on a barrier that is more than one phase behind (parity waits would alias).
+        if (static_cast<int>(it % static_cast<uint32_t>(groups)) != group) continue;
         const uint32_t s = ring.s;
         const uint32_t ph = ring.ph;
         const uint32_t ta = slot.s;
@@ -369,7 +408,7 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         tc_fence_after();
         const uint8_t* a_s = smem_gen + a_base + s * a_bytes;
         const int k0 = kb * tile_k;
-        for (int grp = 0; grp < tile_k / 32; ++grp) {
+        for (int grp = 0; grp < (p.debug_mode == DEBUG_NO_TRANSFORM ? 0 : tile_k / 32); ++grp) {
           const int e0 = grp * 32;        // first k element (within the stage) of this group of 32
           const int chunk = e0 >> 6;      // 64-wide shared-memory chunk
           const int j0 = (e0 & 63) >> 3;  // first 16-byte piece within the row
@@ -378,7 +417,7 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
           for (int mi = 0; mi < M_SUB; ++mi) {
             const uint8_t* rowp = a_s + chunk * (MC * 128) + (mi * 128 + row) * 128;
             uint32_t r[16];
-            float acc = ss[mi];
+            float acc = ss[mi], acc2 = 0.0f;  // two chains halve the dependent-FMA latency
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
               const uint4 v = *reinterpret_cast<const uint4*>(rowp + ((static_cast<uint32_t>(j0 + jj) ^ sw) << 4));
@@ -393,11 +432,11 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                 const float lo = __uint_as_float(w4[w] << 16);
                 const float hi = __uint_as_float(w4[w] & 0xffff0000u);
                 acc = fmaf(lo, lo, acc);
-                acc = fmaf(hi, hi, acc);
+                acc2 = fmaf(hi, hi, acc2);
                 r[jj * 4 + w] = has_gamma ? mul_bf16x2(w4[w], g[w]) : w4[w];
               }
             }
-            ss[mi] = acc;
+            ss[mi] = acc + acc2;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(p.a_col0 + ta * slot_cols + mi * (tile_k / 2) + (e0 >> 1));
             tmem_st_32x32b_x16(taddr, r);
