@@ -41,11 +41,38 @@ def raise_on_status(status: torch.Tensor) -> None:
     """Read a status block back (synchronises) and raise if a device-side wait expired."""
     host = status.cpu().tolist()
     if host[0] != 0:
+        reset_workspaces()
         raise NativeError(
             native.ERR_DEVICE_WAIT,
             f"device-side wait expired: role {host[1]} barrier {host[2]} tile {host[3]} "
             f"k-block {host[4]} CTA {host[5]}",
         )
+
+
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def workspace_for(family: str, M: int, N: int, K: int, device) -> torch.Tensor | None:
+    """Zero-initialised device scratch for kernels that need it (``None`` when they do not).
+
+    The skinny fused kernel keeps its scratch all-zero between launches, so one cached buffer
+    per (device, size) is reused; :func:`reset_workspaces` drops the cache after a failed launch.
+    """
+    need = native.load().b200_workspace_bytes(family.encode(), None, M, N, K)
+    if need == 0:
+        return None
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), int(need))
+    buf = _WORKSPACES.get(key)
+    if buf is None:
+        buf = torch.zeros(int(need), dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def reset_workspaces() -> None:
+    """Forget cached scratch buffers (their contents are undefined after an aborted launch)."""
+    _WORKSPACES.clear()
 
 
 def _ld(t: torch.Tensor) -> int:
@@ -122,10 +149,12 @@ def rmsnorm_matmul(
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     c = Cfg.from_dict(cfg)
+    ws = workspace_for("rmsnorm_matmul", M, N, K, x.device)
     native.check(
         lib.b200_rmsnorm_matmul(
             x.data_ptr(), gamma.data_ptr() if gamma is not None else None, weight.data_ptr(), out.data_ptr(),
-            M, N, K, float(eps), C.byref(c) if c is not None else None, None, 0,
+            M, N, K, float(eps), C.byref(c) if c is not None else None,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
             status.data_ptr() if status is not None else None, _stream_ptr(),
         )
     )
@@ -178,9 +207,11 @@ def time_kernel(
     prob.eps = float(eps)
     ms = (C.c_float * iters)()
     c = Cfg.from_dict(cfg)
+    ws = workspace_for(family, M, N, K, a.device)
     native.check(
         lib.b200_time_kernel(
-            C.byref(prob), C.byref(c) if c is not None else None, None, 0,
+            C.byref(prob), C.byref(c) if c is not None else None,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
             status.data_ptr() if status is not None else None,
             flush.data_ptr() if flush is not None else None,
             flush.numel() * flush.element_size() if flush is not None else 0,

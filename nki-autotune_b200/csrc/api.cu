@@ -12,6 +12,7 @@
 
 #include "gemm_tcgen05.cuh"
 #include "rmsnorm_tcgen05.cuh"
+#include "rmsnorm_skinny.cuh"
 #include "host_api.h"
 
 namespace b200 {
@@ -53,18 +54,22 @@ struct Plan {
   int a_col0, a_slots;  // fused kernel: tensor-memory ring that holds the scaled x tiles
   int a_stages, groups; // fused kernel: shared-memory ring of x tiles; transform warp groups
   long gamma_bytes;     // fused kernel: shared memory reserved for gamma
+  int skinny;           // fused kernel, M <= 16: the weight-streaming swap-AB kernel
   long smem_bytes;
 };
 
-static b200_cfg default_cfg(Family fam) {
+// Best configurations measured on B200 for the benchmark shapes.
+static b200_cfg default_cfg(Family fam, long M) {
   b200_cfg c;
   memset(&c, 0, sizeof(c));
-  c.tile_m = 256;
-  c.tile_n = 256;
-  c.tile_k = 64;
-  c.stages = (fam == FAM_RMSNORM) ? 5 : 6;
-  c.cluster_m = 2;
   c.cluster_n = 1;
+  if (fam == FAM_RMSNORM && M > 0 && M <= 16) {  // weight-streaming kernel
+    c.tile_m = 16; c.tile_n = 128; c.tile_k = 128; c.stages = 6; c.cluster_m = 1;
+  } else if (fam == FAM_RMSNORM) {
+    c.tile_m = 128; c.tile_n = 256; c.tile_k = 128; c.stages = 2; c.cluster_m = 1;
+  } else {
+    c.tile_m = 256; c.tile_n = 256; c.tile_k = 128; c.stages = 3; c.cluster_m = 2;
+  }
   return c;
 }
 
@@ -78,7 +83,30 @@ static int next_pow2_cols(int cols) {
 static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K, Plan* plan) {
   if (fam == FAM_UNKNOWN)
     return set_error(B200_ERR_BAD_ARG, "unknown kernel family (expected matmul_lhsT_rhs or rmsnorm_matmul)");
-  b200_cfg cfg = cfg_in ? *cfg_in : default_cfg(fam);
+  b200_cfg cfg = cfg_in ? *cfg_in : default_cfg(fam, M);
+  if (fam == FAM_RMSNORM && M > 0 && M <= SKINNY_ROWS) {
+    // skinny activations: the weight-streaming kernel; only tile_k and stages apply
+    Plan sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.skinny = 1;
+    sp.cta_group = 1; sp.m_sub = 1; sp.cluster = 1;
+    sp.tile_m = SKINNY_ROWS; sp.tile_n = SKINNY_TILE_N;
+    sp.tile_k = cfg.tile_k; sp.stages = cfg.stages;
+    sp.tmem_cols = 64;
+    if (cfg.tile_k != 64 && cfg.tile_k != 128)
+      return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 are implemented", cfg.tile_k);
+    if (cfg.stages < 1 || cfg.stages > MAX_STAGES)
+      return set_error(B200_ERR_UNSUPPORTED, "stages=%d: need 1..%d", cfg.stages, MAX_STAGES);
+    const long stage = (SKINNY_TILE_N + SKINNY_ROWS) * cfg.tile_k * 2L;
+    sp.smem_bytes = 1024 + cfg.stages * stage + static_cast<long>(sizeof(SkinnyCtrl));
+    *plan = sp;
+    if (sp.smem_bytes > SMEM_BUDGET)
+      return set_error(B200_ERR_SMEM_OOM, "Out of memory in smem: %d stages x %ld B = %ld B > %ld B per CTA",
+                       cfg.stages, stage, sp.smem_bytes, SMEM_BUDGET);
+    if (N <= 0 || K <= 0 || N % 8 != 0 || K % 64 != 0)
+      return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul (skinny): need N %% 8 == 0 and K %% 64 == 0, got N=%ld K=%ld", N, K);
+    return B200_OK;
+  }
   const int cluster_m = cfg.cluster_m == 0 ? 1 : cfg.cluster_m;
   const int cluster_n = cfg.cluster_n == 0 ? 1 : cfg.cluster_n;
   if (cfg.tile_m != 128 && cfg.tile_m != 256)
@@ -256,7 +284,14 @@ struct LaunchArgs {
   void* out;
   long M, N, K, ld_a, ld_b, ld_out;
   float eps;
+  void* workspace;
+  size_t workspace_bytes;
 };
+
+static size_t skinny_workspace_bytes(long N) {
+  const size_t tiles = static_cast<size_t>((N + SKINNY_TILE_N - 1) / SKINNY_TILE_N);
+  return ((static_cast<size_t>(SKINNY_ROWS) * N * sizeof(float) + tiles * sizeof(int)) + 255) & ~static_cast<size_t>(255);
+}
 
 // A prepared launch: tensor maps and parameters are built once and can be replayed.
 struct Prepared {
@@ -265,11 +300,63 @@ struct Prepared {
   CUtensorMap tm_a, tm_b;
   GemmParams gp;
   RmsParams rp;
+  SkinnyParams sp;
   bool fused;
+  bool skinny;
   Plan plan;
   dim3 grid, block;
   size_t smem;
 };
+
+static int prepare_skinny(const LaunchArgs& la, const b200_cfg* cfg, const Plan& plan, const DeviceInfo& di,
+                          int* dev_status, Prepared* pr) {
+  const size_t need = skinny_workspace_bytes(la.N);
+  if (la.workspace == nullptr || la.workspace_bytes < need)
+    return set_error(B200_ERR_WORKSPACE,
+                     "rmsnorm_matmul with M <= 16 needs %zu bytes of zero-initialised device workspace (got %zu)",
+                     need, la.workspace ? la.workspace_bytes : static_cast<size_t>(0));
+  if ((reinterpret_cast<uintptr_t>(la.workspace) & 15u) != 0 || (reinterpret_cast<uintptr_t>(la.a) & 15u) != 0 ||
+      (la.gamma && (reinterpret_cast<uintptr_t>(la.gamma) & 15u) != 0))
+    return set_error(B200_ERR_BAD_ARG, "x, gamma and workspace must be 16-byte aligned");
+  if (la.ld_a != la.K || la.ld_out != la.N)
+    return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul (skinny): x and out must be dense");
+  int rc = make_tmap_bf16(&pr->tm_b, la.b, la.K, la.N, la.ld_b, 64, plan.tile_k, "w");
+  if (rc) return rc;
+  SkinnyParams& sp = pr->sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.M = static_cast<int>(la.M);
+  sp.N = static_cast<int>(la.N);
+  sp.K = static_cast<int>(la.K);
+  sp.tile_k = plan.tile_k;
+  sp.stages = plan.stages;
+  sp.num_n_tiles = static_cast<int>((la.N + SKINNY_TILE_N - 1) / SKINNY_TILE_N);
+  sp.num_k_blocks = static_cast<int>((la.K + plan.tile_k - 1) / plan.tile_k);
+  sp.x = static_cast<const __nv_bfloat16*>(la.a);
+  sp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
+  sp.out = static_cast<__nv_bfloat16*>(la.out);
+  sp.scratch = static_cast<float*>(la.workspace);
+  sp.tile_count = reinterpret_cast<int*>(sp.scratch + static_cast<size_t>(SKINNY_ROWS) * la.N);
+  sp.eps = la.eps;
+  sp.inv_k = 1.0f / static_cast<float>(la.K);
+  sp.status = dev_status;
+  long long limit_us = 1000000;
+  if (cfg && cfg->reserved[1] > 0) limit_us = cfg->reserved[1];
+  sp.timeout_cycles = limit_us * (di.clock_khz > 0 ? di.clock_khz / 1000 : 1900);
+  pr->skinny = true;
+  pr->fused = false;
+  pr->plan = plan;
+  pr->smem = static_cast<size_t>(plan.smem_bytes);
+  pr->block = dim3(SKINNY_THREADS);
+  rc = check_cuda(cudaFuncSetAttribute(reinterpret_cast<const void*>(rmsnorm_skinny_kernel),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pr->smem)),
+                  "cudaFuncSetAttribute(max dynamic shared memory)");
+  if (rc) return rc;
+  long long units = static_cast<long long>(sp.num_n_tiles) * sp.num_k_blocks;
+  long long grid = di.sm_count;
+  if (grid > units) grid = units;
+  pr->grid = dim3(static_cast<unsigned>(grid));
+  return B200_OK;
+}
 
 static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, Prepared* pr) {
   if (!la.a || !la.b || !la.out) return set_error(B200_ERR_BAD_ARG, "NULL operand pointer");
@@ -279,6 +366,8 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   DeviceInfo di;
   rc = device_info(&di);
   if (rc) return rc;
+  pr->skinny = false;
+  if (plan.skinny) return prepare_skinny(la, cfg, plan, di, dev_status, pr);
   if ((reinterpret_cast<uintptr_t>(la.out) & 15u) != 0 || la.ld_out % 8 != 0 || la.ld_out < la.N)
     return set_error(B200_ERR_BAD_SHAPE, "out: pointer must be 16-byte aligned and ld_out a multiple of 8 >= N");
   if (la.gamma && (reinterpret_cast<uintptr_t>(la.gamma) & 15u) != 0)
@@ -396,6 +485,8 @@ static int launch(const Prepared& pr, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
+  if (pr.skinny)
+    return check_cuda(cudaLaunchKernelEx(&lc, rmsnorm_skinny_kernel, pr.tm_b, pr.sp), "skinny RMSNorm GEMM launch");
   if (pr.fused)
     return check_cuda(cudaLaunchKernelEx(&lc, pr.rms_fn, pr.tm_a, pr.tm_b, pr.rp), "fused RMSNorm GEMM launch");
   return check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.gp), "tcgen05 GEMM launch");
@@ -432,16 +523,16 @@ extern "C" int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, l
 }
 
 extern "C" size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K) {
-  (void)family; (void)cfg; (void)M; (void)N; (void)K;
+  (void)cfg; (void)K;
+  if (parse_family(family) == FAM_RMSNORM && M > 0 && M <= SKINNY_ROWS && N > 0) return skinny_workspace_bytes(N);
   return 0;
 }
 
 extern "C" int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out, long M, long N, long K,
                                     long ld_lhsT, long ld_rhs, long ld_out, const b200_cfg* cfg, void* workspace,
                                     size_t workspace_bytes, int* dev_status, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   LaunchArgs la{FAM_LHST, lhsT, rhs, nullptr, out, M, N, K, ld_lhsT ? ld_lhsT : M, ld_rhs ? ld_rhs : N,
-                ld_out ? ld_out : N, 0.0f};
+                ld_out ? ld_out : N, 0.0f, workspace, workspace_bytes};
   Prepared pr;
   int rc = prepare(la, cfg, dev_status, &pr);
   if (rc) return rc;
@@ -451,8 +542,7 @@ extern "C" int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out
 extern "C" int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out, long M, long N,
                                    long K, float eps, const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
                                    int* dev_status, void* stream) {
-  (void)workspace; (void)workspace_bytes;
-  LaunchArgs la{FAM_RMSNORM, x, w, gamma, out, M, N, K, K, N, N, eps};
+  LaunchArgs la{FAM_RMSNORM, x, w, gamma, out, M, N, K, K, N, N, eps, workspace, workspace_bytes};
   Prepared pr;
   int rc = prepare(la, cfg, dev_status, &pr);
   if (rc) return rc;
@@ -462,7 +552,6 @@ extern "C" int b200_rmsnorm_matmul(const void* x, const void* gamma, const void*
 extern "C" int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
                                 int* dev_status, void* flush_buf, size_t flush_bytes, int warmup, int iters,
                                 float* ms_each, void* stream_v) {
-  (void)workspace; (void)workspace_bytes;
   if (!p || !ms_each || iters <= 0 || warmup < 0) return set_error(B200_ERR_BAD_ARG, "time_kernel: bad arguments");
   Family fam = parse_family(p->family);
   if (fam == FAM_UNKNOWN) return set_error(B200_ERR_BAD_ARG, "time_kernel: unknown family");
@@ -479,6 +568,8 @@ extern "C" int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg, void
   la.ld_b = p->ld_b ? p->ld_b : p->N;
   la.ld_out = p->ld_out ? p->ld_out : p->N;
   la.eps = p->eps;
+  la.workspace = workspace;
+  la.workspace_bytes = workspace_bytes;
   Prepared pr;
   int rc = prepare(la, cfg, dev_status, &pr);
   if (rc) return rc;

@@ -1,0 +1,355 @@
+// Fused RMSNorm + matmul for skinny activations (M <= 16 rows, e.g. decode):
+//     out[M,N] = (x / rms(x) * gamma)[M,K] . w[K,N]
+// The work is streaming w (K*N*2 bytes) once from HBM, so the kernel is built around that:
+//
+//   * swap-AB: the UMMA computes out^T tiles, D[128 n, 16 m] += W^T[128 n, k] . xg^T[k, 16 m], so the
+//     128-wide MMA M dimension is filled by weight columns and the 16 activation rows sit on N.
+//     A = w tile [tile_k x 128] (MN-major, straight from TMA), B = xg tile [16 x tile_k] (K-major).
+//   * stream-K: the (n-tile, k-block) units are flattened and cut into one contiguous range per
+//     CTA, so all SMs stream equal amounts of w whatever N/128 is.  A CTA that covers only part
+//     of a tile's K adds its fp32 partial into a scratch array with atomics; the warp that
+//     completes a tile's count scales by rinv[m], writes bf16 and zeroes the scratch again.
+//   * x is tiny (M*K): four warps stage x*gamma tiles into shared memory in the swizzled
+//     K-major layout the UMMA reads, and every CTA computes rinv[m] for itself from x (L2).
+//
+// Same maths as kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 (plus gamma); the
+// per-row factor is applied after the K sum.  All waits are bounded (see gemm_tcgen05.cuh).
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace b200 {
+
+constexpr int SKINNY_ROWS = 16;       // activation rows per launch (UMMA N)
+constexpr int SKINNY_TILE_N = 128;    // weight columns per tile (UMMA M)
+constexpr int SKINNY_ACC_BUFS = 4;    // 16-column accumulators in tensor memory
+constexpr int SKINNY_THREADS = 32 * 10;
+
+struct SkinnyParams {
+  int M, N, K;
+  int tile_k, stages;
+  int num_n_tiles, num_k_blocks;
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* gamma;   // may be nullptr
+  __nv_bfloat16* out;
+  float* scratch;               // [16][N] fp32 partial sums, all zero between launches
+  int* tile_count;              // [num_n_tiles] contributions seen, all zero between launches
+  float eps, inv_k;
+  int* status;
+  long long timeout_cycles;
+};
+
+struct alignas(16) SkinnyCtrl {
+  uint64_t full_w[MAX_STAGES];   // w tile of stage s has landed
+  uint64_t full_x[MAX_STAGES];   // scaled x tile of stage s has been written
+  uint64_t empty[MAX_STAGES];    // UMMAs reading stage s have finished
+  uint64_t acc_full[SKINNY_ACC_BUFS];
+  uint64_t acc_empty[SKINNY_ACC_BUFS];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  float rinv[SKINNY_ROWS];
+};
+
+struct SkinnyWait {
+  SkinnyCtrl* ctrl;
+  int* status;
+  long long limit;
+  int role;
+};
+
+__device__ __forceinline__ bool skinny_wait(const SkinnyWait& w, uint32_t bar, uint32_t parity, int bar_id,
+                                            int unit) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (w.ctrl->abort_flag) return false;
+      if (clock64() - t0 > w.limit) {
+        w.ctrl->abort_flag = 1;
+        if (w.status != nullptr && atomicCAS(w.status, 0, 7) == 0) {
+          w.status[1] = w.role;
+          w.status[2] = bar_id;
+          w.status[3] = unit;
+          w.status[5] = static_cast<int>(blockIdx.x);
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(SKINNY_THREADS, 1)
+rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tile_k = p.tile_k;
+  const int stages = p.stages;
+  const uint32_t w_bytes = static_cast<uint32_t>(SKINNY_TILE_N) * tile_k * 2u;
+  const uint32_t x_bytes = static_cast<uint32_t>(SKINNY_ROWS) * tile_k * 2u;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t w_base = smem_base;
+  const uint32_t x_base = w_base + stages * w_bytes;
+  const uint32_t ctrl_addr = x_base + stages * x_bytes;
+  uint8_t* const smem_gen = smem_raw - smem_u32(smem_raw);
+  SkinnyCtrl* ctrl = reinterpret_cast<SkinnyCtrl*>(smem_gen + ctrl_addr);
+
+  // this CTA's contiguous range of (n-tile, k-block) units
+  const int nkb = p.num_k_blocks;
+  const long long total_units = static_cast<long long>(p.num_n_tiles) * nkb;
+  const long long u_begin = total_units * blockIdx.x / gridDim.x;
+  const long long u_end = total_units * (blockIdx.x + 1) / gridDim.x;
+
+  if (threadIdx.x == 0) {
+    ctrl->abort_flag = 0;
+    tma_prefetch_desc(&tm_w);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full_w[s]), 1);
+      mbar_init(smem_u32(&ctrl->full_x[s]), 4);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int b = 0; b < SKINNY_ACC_BUFS; ++b) {
+      mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
+      mbar_init(smem_u32(&ctrl->acc_empty[b]), 4);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(&ctrl->tmem_base), 64);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  SkinnyWait wctx{ctrl, p.status, p.timeout_cycles, 0};
+
+  // ------------------------------------------------------------------ TMA producer (w tiles)
+  if (warp == 0) {
+    if (lane == 0) {
+      wctx.role = ROLE_PRODUCER;
+      Ring ring;
+      bool ok = true;
+      for (long long u = u_begin; u < u_end && ok; ++u, ring.advance(stages)) {
+        const int nt = static_cast<int>(u / nkb);
+        const int kb = static_cast<int>(u - static_cast<long long>(nt) * nkb);
+        ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 100 + ring.s, static_cast<int>(u - u_begin));
+        if (!ok) break;
+        const uint32_t w_s = w_base + ring.s * w_bytes;
+        const uint32_t fw = smem_u32(&ctrl->full_w[ring.s]);
+        mbar_arrive_expect_tx(fw, w_bytes);
+        tma_load_2d(w_s, &tm_w, fw, nt * SKINNY_TILE_N, kb * tile_k);
+        tma_load_2d(w_s + tile_k * 128, &tm_w, fw, nt * SKINNY_TILE_N + 64, kb * tile_k);
+      }
+      for (int i = 0; i < stages && ok; ++i, ring.advance(stages))
+        ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1);
+    }
+    __syncwarp();
+  }
+  // ------------------------------------------------------------------ UMMA issuer
+  else if (warp == 1) {
+    if (lane == 0) {
+      wctx.role = ROLE_MMA;
+      const uint32_t idesc = make_idesc_bf16_f32(128, SKINNY_ROWS, 1, 0);  // A MN-major, B K-major
+      const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
+      const uint64_t a_desc0 = make_smem_desc_sw128(w_base, mn_lbo, 1024);
+      const int nk16 = tile_k / 16;
+      Ring ring, acc;
+      bool ok = true;
+      long long u = u_begin;
+      while (u < u_end && ok) {
+        const int nt = static_cast<int>(u / nkb);
+        const long long seg_end = min(u_end, static_cast<long long>(nt + 1) * nkb);
+        ok = skinny_wait(wctx, smem_u32(&ctrl->acc_empty[acc.s]), acc.ph ^ 1u, 200 + acc.s, static_cast<int>(u - u_begin));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc.s * SKINNY_ROWS;
+        bool first = true;
+        for (; u < seg_end; ++u, ring.advance(stages)) {
+          const uint32_t s = ring.s;
+          ok = skinny_wait(wctx, smem_u32(&ctrl->full_w[s]), ring.ph, 300 + s, static_cast<int>(u - u_begin));
+          if (ok) ok = skinny_wait(wctx, smem_u32(&ctrl->full_x[s]), ring.ph, 400 + s, static_cast<int>(u - u_begin));
+          if (!ok) break;
+          tc_fence_after();
+          uint64_t adesc = a_desc0 + s * (w_bytes >> 4);
+          const uint32_t x_s = x_base + s * x_bytes;
+          for (int k16 = 0; k16 < nk16; ++k16, adesc += 128) {
+            const uint64_t bdesc =
+                make_smem_desc_sw128(x_s + (k16 >> 2) * (SKINNY_ROWS * 128) + (k16 & 3) * 32, 16, 1024);
+            umma_bf16<1>(d_tmem, adesc, bdesc, idesc, first ? 0u : 1u);
+            first = false;
+          }
+          umma_commit_1cta(smem_u32(&ctrl->empty[s]));
+        }
+        if (!ok) break;
+        umma_commit_1cta(smem_u32(&ctrl->acc_full[acc.s]));
+        acc.advance(SKINNY_ACC_BUFS);
+      }
+    }
+    __syncwarp();
+  }
+  // ------------------------------------------------------------------ epilogue warps
+  else if (warp < 6) {
+    wctx.role = ROLE_EPILOGUE;
+    const int q = warp & 3;          // tensor-memory lane quadrant
+    const int et = (warp - 2) * 32 + lane;  // 0..127
+    // rinv[m] for every row, from x itself: 8 threads per row, 16-byte loads, shuffle reduction
+    {
+      const int row = et >> 3, part = et & 7;
+      float ss = 0.0f;
+      if (row < p.M) {
+        const int per = p.K / 8;  // K is a multiple of 64
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K + part * per);
+        for (int i = 0; i < per / 8; ++i) {
+          const uint4 v = __ldg(src + i);
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
+            ss = fmaf(lo, lo, ss);
+            ss = fmaf(hi, hi, ss);
+          }
+        }
+      }
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      if (part == 0) ctrl->rinv[row] = (row < p.M) ? rsqrtf(ss * p.inv_k + p.eps) : 0.0f;
+      // the four epilogue warps meet here once, before any bounded wait (no early exit possible)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    Ring acc;
+    bool ok = true;
+    long long u = u_begin;
+    while (u < u_end && ok) {
+      const int nt = static_cast<int>(u / nkb);
+      const long long seg_end = min(u_end, static_cast<long long>(nt + 1) * nkb);
+      const int seg_blocks = static_cast<int>(seg_end - u);
+      ok = skinny_wait(wctx, smem_u32(&ctrl->acc_full[acc.s]), acc.ph, 500 + acc.s, static_cast<int>(u - u_begin));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v[16];
+      tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc.s * SKINNY_ROWS, v);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[acc.s]));
+      const int n = nt * SKINNY_TILE_N + q * 32 + lane;
+      if (seg_blocks == nkb) {
+        // this CTA summed the whole K range of the tile: no scratch traffic at all
+        if (n < p.N) {
+#pragma unroll
+          for (int m = 0; m < SKINNY_ROWS; ++m)
+            if (m < p.M)
+              p.out[static_cast<long long>(m) * p.N + n] = __float2bfloat16(__uint_as_float(v[m]) * ctrl->rinv[m]);
+        }
+      } else {
+        if (n < p.N) {
+#pragma unroll
+          for (int m = 0; m < SKINNY_ROWS; ++m)
+            if (m < p.M) atomicAdd(p.scratch + static_cast<long long>(m) * p.N + n, __uint_as_float(v[m]));
+        }
+        __threadfence();
+        __syncwarp();
+        int seen = 0;
+        if (lane == 0) seen = atomicAdd(p.tile_count + nt, seg_blocks) + seg_blocks;
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (seen == 4 * nkb) {
+          // last of the (4 warps x all CTAs) contributions: every partial is visible; finish the
+          // whole 128-column tile and leave scratch and counter zero for the next launch
+          __threadfence();
+          for (int c = 0; c < 4; ++c) {
+            const int nn = nt * SKINNY_TILE_N + c * 32 + lane;
+            if (nn < p.N)
+              for (int m = 0; m < p.M; ++m) {
+                float* cell = p.scratch + static_cast<long long>(m) * p.N + nn;
+                const float sum = __ldcg(cell);
+                p.out[static_cast<long long>(m) * p.N + nn] = __float2bfloat16(sum * ctrl->rinv[m]);
+                __stcg(cell, 0.0f);
+              }
+          }
+          if (lane == 0) p.tile_count[nt] = 0;
+        }
+      }
+      u = seg_end;
+      acc.advance(SKINNY_ACC_BUFS);
+    }
+  }
+  // ------------------------------------------------------------------ x-tile staging warps
+  else {
+    wctx.role = ROLE_TRANSFORM;
+    const int tt = (warp - 6) * 32 + lane;  // 0..127
+    const int pieces_per_row = tile_k / 8;  // 16-byte pieces of one row of a stage
+    const int pieces = SKINNY_ROWS * pieces_per_row;  // 128 (tile_k 64) or 256 (tile_k 128)
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 one4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
+    // x and gamma pieces of unit u; loads are issued one unit ahead of their use so that the
+    // L2 latency overlaps the previous stage instead of adding to every stage
+    auto load_unit = [&](long long u, uint4 (&xv)[2], uint4 (&gv)[2]) {
+      const int nt = static_cast<int>(u / nkb);
+      const int kb = static_cast<int>(u - static_cast<long long>(nt) * nkb);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c = tt + i * 128;
+        xv[i] = zero4;
+        gv[i] = one4;
+        if (c < pieces) {
+          const int row = c / pieces_per_row;
+          const int k = kb * tile_k + (c - row * pieces_per_row) * 8;
+          if (row < p.M && k < p.K) {
+            xv[i] = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K + k));
+            if (p.gamma != nullptr) gv[i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + k));
+          }
+        }
+      }
+    };
+    uint4 cur_x[2], cur_g[2], nxt_x[2], nxt_g[2];
+    if (u_begin < u_end) load_unit(u_begin, cur_x, cur_g);
+    Ring ring;
+    bool ok = true;
+    for (long long u = u_begin; u < u_end && ok; ++u, ring.advance(stages)) {
+      if (u + 1 < u_end) load_unit(u + 1, nxt_x, nxt_g);
+      ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 700 + ring.s, static_cast<int>(u - u_begin));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      uint8_t* x_s = smem_gen + x_base + ring.s * x_bytes;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c = tt + i * 128;
+        if (c < pieces) {
+          const int row = c / pieces_per_row;
+          const int j = c - row * pieces_per_row;   // 16-byte piece along k within the stage
+          uint4 o;
+          o.x = mul_bf16x2(cur_x[i].x, cur_g[i].x); o.y = mul_bf16x2(cur_x[i].y, cur_g[i].y);
+          o.z = mul_bf16x2(cur_x[i].z, cur_g[i].z); o.w = mul_bf16x2(cur_x[i].w, cur_g[i].w);
+          // K-major, 128-byte swizzle: 64-wide chunk (j / 8), row, piece (j % 8) xor (row % 8)
+          uint8_t* dst = x_s + (j >> 3) * (SKINNY_ROWS * 128) + row * 128 +
+                         ((static_cast<uint32_t>(j & 7) ^ static_cast<uint32_t>(row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = o;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->full_x[ring.s]));
+#pragma unroll
+      for (int i = 0; i < 2; ++i) { cur_x[i] = nxt_x[i]; cur_g[i] = nxt_g[i]; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (ctrl->abort_flag && threadIdx.x == 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, 64);
+  }
+}
+
+}  // namespace b200

@@ -108,11 +108,6 @@ __device__ __forceinline__ bool rms_wait(const RmsWait& w, uint32_t bar, uint32_
   return true;
 }
 
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-
 template <int CTA_GROUP, int M_SUB>
 __global__ void __launch_bounds__(RMS_THREADS, 1)
 rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,

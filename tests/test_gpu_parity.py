@@ -190,6 +190,42 @@ def test_fused_matches_fp32_device_crosscheck(K):
     assert O.max_abs_rel_err(K.to_host(out).astype(np.float32), K.to_host(ref)) <= TOL_BF16
 
 
+# ---- skinny activations: weight-streaming kernel with scratch ----------------------------------
+@pytest.mark.parametrize("m,k,n", [(16, 64, 128), (16, 1024, 512), (8, 256, 200), (1, 512, 1024), (16, 4096, 4096), (12, 2048, 3080)])
+@pytest.mark.parametrize("c", [cfg(16, 128, 64, 3), cfg(16, 128, 128, 2), None], ids=["tk64", "tk128", "default"])
+def test_rmsnorm_skinny_shapes(K, m, k, n, c):
+    eps = 1e-5
+    for _ in range(2):  # the second call runs on the scratch the first one left behind
+        got, expect = _rms_case(K, 21, m, k, n, eps, c)
+        assert O.max_abs_rel_err(got, expect) <= TOL_BF16
+
+
+def test_rmsnorm_skinny_scratch_is_left_zero(K):
+    import torch
+
+    _rms_case(K, 22, 16, 2048, 4096, 1e-5, None)
+    ws = K.workspace_for("rmsnorm_matmul", 16, 4096, 2048, "cuda")
+    torch.cuda.synchronize()
+    assert ws is not None and int((ws != 0).sum()) == 0
+
+
+def test_rmsnorm_skinny_without_workspace_is_an_error(K):
+    """Straight through the C ABI: the skinny kernel refuses to run without its scratch."""
+    import torch
+
+    from autotune import native
+
+    lib = native.load()
+    x = torch.zeros(16, 256, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(16, 256, dtype=torch.bfloat16, device="cuda")
+    rc = lib.b200_rmsnorm_matmul(x.data_ptr(), None, w.data_ptr(), out.data_ptr(), 16, 256, 256, 1e-5, None, None, 0, None,
+                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == native.ERR_WORKSPACE and "workspace" in native.last_error()
+    assert lib.b200_workspace_bytes(b"rmsnorm_matmul", None, 16, 256, 256) >= 16 * 256 * 4
+    assert lib.b200_workspace_bytes(b"rmsnorm_matmul", None, 4096, 256, 256) == 0
+
+
 # ---- argument checking and bounded waits -------------------------------------------------------
 def test_bad_arguments_raise(K):
     import torch
