@@ -64,7 +64,7 @@ static b200_cfg default_cfg(Family fam, long M) {
   memset(&c, 0, sizeof(c));
   c.cluster_n = 1;
   if (fam == FAM_RMSNORM && M > 0 && M <= 16) {  // weight-streaming kernel
-    c.tile_m = 16; c.tile_n = 128; c.tile_k = 128; c.stages = 6; c.cluster_m = 1;
+    c.tile_m = 16; c.tile_n = 256; c.tile_k = 128; c.stages = 3; c.cluster_m = 1;
   } else if (fam == FAM_RMSNORM) {
     c.tile_m = 128; c.tile_n = 256; c.tile_k = 128; c.stages = 2; c.cluster_m = 1;
   } else {
@@ -92,7 +92,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     sp.cta_group = 1; sp.m_sub = 1; sp.cluster = 1;
     sp.tile_m = SKINNY_ROWS; sp.tile_n = SKINNY_TILE_N;
     sp.tile_k = cfg.tile_k; sp.stages = cfg.stages;
-    sp.tmem_cols = 64;
+    sp.tmem_cols = SKINNY_TMEM_COLS;
     if (cfg.tile_k != 64 && cfg.tile_k != 128)
       return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 are implemented", cfg.tile_k);
     if (cfg.stages < 1 || cfg.stages > MAX_STAGES)

@@ -2,15 +2,18 @@
 //     out[M,N] = (x / rms(x) * gamma)[M,K] . w[K,N]
 // The work is streaming w (K*N*2 bytes) once from HBM, so the kernel is built around that:
 //
-//   * swap-AB: the UMMA computes out^T tiles, D[128 n, 16 m] += W^T[128 n, k] . xg^T[k, 16 m], so the
-//     128-wide MMA M dimension is filled by weight columns and the 16 activation rows sit on N.
-//     A = w tile [tile_k x 128] (MN-major, straight from TMA), B = xg tile [16 x tile_k] (K-major).
+//   * one UMMA per 16 k covers 256 weight columns: D[128, 256 n] += A[128, 16 k] . B[16 k, 256 n]
+//     with B = w tile (MN-major, straight from TMA) and A = the scaled x tile (K-major).  Only
+//     rows 0..15 of A exist: the descriptor's row groups beyond them read whatever follows in
+//     shared memory, which only pollutes accumulator rows 16..127 -- rows of D are independent
+//     and those rows are never read.
 //   * stream-K: the (n-tile, k-block) units are flattened and cut into one contiguous range per
 //     CTA, so all SMs stream equal amounts of w whatever N/128 is.  A CTA that covers only part
 //     of a tile's K adds its fp32 partial into a scratch array with atomics; the warp that
 //     completes a tile's count scales by rinv[m], writes bf16 and zeroes the scratch again.
 //   * x is tiny (M*K): four warps stage x*gamma tiles into shared memory in the swizzled
-//     K-major layout the UMMA reads, and every CTA computes rinv[m] for itself from x (L2).
+//     K-major layout the UMMA reads (loads issued one unit ahead), and every CTA computes
+//     rinv[m] for itself from x (L2).
 //
 // Same maths as kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 (plus gamma); the
 // per-row factor is applied after the K sum.  All waits are bounded (see gemm_tcgen05.cuh).
@@ -19,9 +22,10 @@
 
 namespace b200 {
 
-constexpr int SKINNY_ROWS = 16;       // activation rows per launch (UMMA N)
-constexpr int SKINNY_TILE_N = 128;    // weight columns per tile (UMMA M)
-constexpr int SKINNY_ACC_BUFS = 4;    // 16-column accumulators in tensor memory
+constexpr int SKINNY_ROWS = 16;       // activation rows per launch (rows 0..15 of the UMMA M side)
+constexpr int SKINNY_TILE_N = 256;    // weight columns per tile (UMMA N): 512 contiguous bytes per k-row
+constexpr int SKINNY_ACC_BUFS = 2;    // 256-column accumulators in tensor memory
+constexpr int SKINNY_TMEM_COLS = SKINNY_ACC_BUFS * SKINNY_TILE_N;
 constexpr int SKINNY_THREADS = 32 * 10;
 
 struct SkinnyParams {
@@ -90,9 +94,10 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   const uint32_t w_bytes = static_cast<uint32_t>(SKINNY_TILE_N) * tile_k * 2u;
   const uint32_t x_bytes = static_cast<uint32_t>(SKINNY_ROWS) * tile_k * 2u;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t w_base = smem_base;
-  const uint32_t x_base = w_base + stages * w_bytes;
-  const uint32_t ctrl_addr = x_base + stages * x_bytes;
+  // x stages first: the UMMA's reads past row 15 of an x tile then land in the w stages
+  const uint32_t x_base = smem_base;
+  const uint32_t w_base = x_base + stages * x_bytes;
+  const uint32_t ctrl_addr = w_base + stages * w_bytes;
   uint8_t* const smem_gen = smem_raw - smem_u32(smem_raw);
   SkinnyCtrl* ctrl = reinterpret_cast<SkinnyCtrl*>(smem_gen + ctrl_addr);
 
@@ -112,12 +117,12 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
     }
     for (int b = 0; b < SKINNY_ACC_BUFS; ++b) {
       mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[b]), 4);
+      mbar_init(smem_u32(&ctrl->acc_empty[b]), 1);
     }
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(&ctrl->tmem_base), 64);
+    tmem_alloc<1>(smem_u32(&ctrl->tmem_base), SKINNY_TMEM_COLS);
     tmem_relinquish<1>();
   }
   tc_fence_before();
@@ -140,8 +145,8 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         const uint32_t w_s = w_base + ring.s * w_bytes;
         const uint32_t fw = smem_u32(&ctrl->full_w[ring.s]);
         mbar_arrive_expect_tx(fw, w_bytes);
-        tma_load_2d(w_s, &tm_w, fw, nt * SKINNY_TILE_N, kb * tile_k);
-        tma_load_2d(w_s + tile_k * 128, &tm_w, fw, nt * SKINNY_TILE_N + 64, kb * tile_k);
+        for (int c = 0; c < SKINNY_TILE_N / 64; ++c)
+          tma_load_2d(w_s + c * tile_k * 128, &tm_w, fw, nt * SKINNY_TILE_N + 64 * c, kb * tile_k);
       }
       for (int i = 0; i < stages && ok; ++i, ring.advance(stages))
         ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1);
@@ -152,9 +157,9 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   else if (warp == 1) {
     if (lane == 0) {
       wctx.role = ROLE_MMA;
-      const uint32_t idesc = make_idesc_bf16_f32(128, SKINNY_ROWS, 1, 0);  // A MN-major, B K-major
+      const uint32_t idesc = make_idesc_bf16_f32(128, SKINNY_TILE_N, 0, 1);  // A K-major, B MN-major
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
-      const uint64_t a_desc0 = make_smem_desc_sw128(w_base, mn_lbo, 1024);
+      const uint64_t b_desc0 = make_smem_desc_sw128(w_base, mn_lbo, 1024);
       const int nk16 = tile_k / 16;
       Ring ring, acc;
       bool ok = true;
@@ -165,7 +170,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         ok = skinny_wait(wctx, smem_u32(&ctrl->acc_empty[acc.s]), acc.ph ^ 1u, 200 + acc.s, static_cast<int>(u - u_begin));
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc.s * SKINNY_ROWS;
+        const uint32_t d_tmem = tmem_base + acc.s * SKINNY_TILE_N;
         bool first = true;
         for (; u < seg_end; ++u, ring.advance(stages)) {
           const uint32_t s = ring.s;
@@ -173,10 +178,10 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
           if (ok) ok = skinny_wait(wctx, smem_u32(&ctrl->full_x[s]), ring.ph, 400 + s, static_cast<int>(u - u_begin));
           if (!ok) break;
           tc_fence_after();
-          uint64_t adesc = a_desc0 + s * (w_bytes >> 4);
+          uint64_t bdesc = b_desc0 + s * (w_bytes >> 4);
           const uint32_t x_s = x_base + s * x_bytes;
-          for (int k16 = 0; k16 < nk16; ++k16, adesc += 128) {
-            const uint64_t bdesc =
+          for (int k16 = 0; k16 < nk16; ++k16, bdesc += 128) {
+            const uint64_t adesc =
                 make_smem_desc_sw128(x_s + (k16 >> 2) * (SKINNY_ROWS * 128) + (k16 & 3) * 32, 16, 1024);
             umma_bf16<1>(d_tmem, adesc, bdesc, idesc, first ? 0u : 1u);
             first = false;
@@ -202,14 +207,19 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       if (row < p.M) {
         const int per = p.K / 8;  // K is a multiple of 64
         const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K + part * per);
-        for (int i = 0; i < per / 8; ++i) {
-          const uint4 v = __ldg(src + i);
-          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+        for (int i0 = 0; i0 < per / 8; i0 += 8) {  // eight independent 16-byte loads in flight
+          uint4 v8[8];
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
-            ss = fmaf(lo, lo, ss);
-            ss = fmaf(hi, hi, ss);
+          for (int i = 0; i < 8; ++i) v8[i] = (i0 + i < per / 8) ? __ldg(src + i0 + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t w4[4] = {v8[i].x, v8[i].y, v8[i].z, v8[i].w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
+              ss = fmaf(lo, lo, ss);
+              ss = fmaf(hi, hi, ss);
+            }
           }
         }
       }
@@ -220,8 +230,10 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       // the four epilogue warps meet here once, before any bounded wait (no early exit possible)
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
+    // Accumulator rows 0..15 (tensor-memory lanes 0..15) hold the result; only the warp that owns
+    // lane quadrant 0 can read them, so it alone drains: lane m holds out[m, n0 .. n0+255].
     Ring acc;
-    bool ok = true;
+    bool ok = (q == 0);
     long long u = u_begin;
     while (u < u_end && ok) {
       const int nt = static_cast<int>(u / nkb);
@@ -231,45 +243,61 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t v[16];
-      tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc.s * SKINNY_ROWS, v);
-      tmem_ld_wait();
+      const int n0 = nt * SKINNY_TILE_N;
+      const bool whole_k = (seg_blocks == nkb);  // this CTA summed the tile's whole K range
+      const float my_rinv = ctrl->rinv[lane & 15];
+      for (int c = 0; c < SKINNY_TILE_N / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + acc.s * SKINNY_TILE_N + c * 32, v);
+        tmem_ld_wait();
+        if (lane < p.M) {
+          const long long base = static_cast<long long>(lane) * p.N + n0 + c * 32;
+          if (whole_k) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+              if (n0 + c * 32 + j < p.N)  // N is even
+                *reinterpret_cast<uint32_t*>(p.out + base + j) =
+                    pack_bf16x2(__uint_as_float(v[j]) * my_rinv, __uint_as_float(v[j + 1]) * my_rinv);
+          } else {
+            // 16-byte vector reductions: N is a multiple of 8, so a group of four never straddles N
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (n0 + c * 32 + j < p.N)
+                atomicAdd(reinterpret_cast<float4*>(p.scratch + base + j),
+                          make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                      __uint_as_float(v[j + 3])));
+          }
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[acc.s]));
-      const int n = nt * SKINNY_TILE_N + q * 32 + lane;
-      if (seg_blocks == nkb) {
-        // this CTA summed the whole K range of the tile: no scratch traffic at all
-        if (n < p.N) {
-#pragma unroll
-          for (int m = 0; m < SKINNY_ROWS; ++m)
-            if (m < p.M)
-              p.out[static_cast<long long>(m) * p.N + n] = __float2bfloat16(__uint_as_float(v[m]) * ctrl->rinv[m]);
-        }
-      } else {
-        if (n < p.N) {
-#pragma unroll
-          for (int m = 0; m < SKINNY_ROWS; ++m)
-            if (m < p.M) atomicAdd(p.scratch + static_cast<long long>(m) * p.N + n, __uint_as_float(v[m]));
-        }
+      if (!whole_k) {
         __threadfence();
         __syncwarp();
         int seen = 0;
         if (lane == 0) seen = atomicAdd(p.tile_count + nt, seg_blocks) + seg_blocks;
         seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (seen == 4 * nkb) {
-          // last of the (4 warps x all CTAs) contributions: every partial is visible; finish the
-          // whole 128-column tile and leave scratch and counter zero for the next launch
+        if (seen == nkb) {
+          // last contribution to this tile: every partial is visible; scale, store, and leave
+          // scratch and counter zero for the next launch
           __threadfence();
-          for (int c = 0; c < 4; ++c) {
-            const int nn = nt * SKINNY_TILE_N + c * 32 + lane;
-            if (nn < p.N)
-              for (int m = 0; m < p.M; ++m) {
-                float* cell = p.scratch + static_cast<long long>(m) * p.N + nn;
-                const float sum = __ldcg(cell);
-                p.out[static_cast<long long>(m) * p.N + nn] = __float2bfloat16(sum * ctrl->rinv[m]);
-                __stcg(cell, 0.0f);
-              }
+          // all 16 loads of a column are issued before the first store: the loop is otherwise
+          // one L2 round trip per cell (loads cannot be hoisted over possibly-aliasing stores)
+          for (int c = 0; c < SKINNY_TILE_N / 32; ++c) {
+            const int nn = n0 + c * 32 + lane;
+            if (nn < p.N) {
+              float sums[SKINNY_ROWS];
+#pragma unroll
+              for (int m = 0; m < SKINNY_ROWS; ++m)
+                sums[m] = (m < p.M) ? __ldcg(p.scratch + static_cast<long long>(m) * p.N + nn) : 0.0f;
+#pragma unroll
+              for (int m = 0; m < SKINNY_ROWS; ++m)
+                if (m < p.M) {
+                  p.out[static_cast<long long>(m) * p.N + nn] = __float2bfloat16(sums[m] * ctrl->rinv[m]);
+                  __stcg(p.scratch + static_cast<long long>(m) * p.N + nn, 0.0f);
+                }
+            }
           }
           if (lane == 0) p.tile_count[nt] = 0;
         }
@@ -348,7 +376,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, 64);
+    tmem_dealloc<1>(tmem_base, SKINNY_TMEM_COLS);
   }
 }
 
