@@ -105,6 +105,24 @@ int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* o
                         const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
                         int* dev_status, void* stream);
 
+/* Largest N served by b200_rmsnorm_matmul_noalloc. */
+#define B200_NOALLOC_MAX_N 32768
+
+/* The M <= 16 case of b200_rmsnorm_matmul for callers that cannot allocate device memory at the
+ * call site (an engine that has handed the whole device heap to its own pools, a thread that
+ * must stay out of the allocator's locks): the kernel's scratch lives in a static device array
+ * inside the library (16 x B200_NOALLOC_MAX_N floats + counters, about 2 MB, held by every GPU
+ * that loads the library until the process exits) instead of a caller workspace.  No cudaMalloc,
+ * cudaFree or other allocating call is made.  Requires 1 <= M <= 16 and N <= B200_NOALLOC_MAX_N
+ * (otherwise B200_ERR_BAD_SHAPE).  The first call on each device resolves the array's device
+ * address; make that call outside any stream capture.  All calls on a device share the one
+ * array: each call clears the part it uses on `stream` first, and two calls that can overlap
+ * on the GPU (different streams without ordering) race and give wrong results.
+ * No counterpart in the reference. */
+int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, const void* w, void* out,
+                                long M, long N, long K, float eps, const b200_cfg* cfg,
+                                int* dev_status, void* stream);
+
 /* fp32 CUDA-core evaluation of the same fused expression on bf16 inputs (fp32 output),
  * used as the on-device cross-check of b200_rmsnorm_matmul. */
 int b200_rmsnorm_matmul_f32(const void* x, const void* gamma, const void* w, void* out_f32,

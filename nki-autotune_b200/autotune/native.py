@@ -97,6 +97,11 @@ SIGNATURES = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_float,
          C.POINTER(Cfg), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p],
     ),
+    "b200_rmsnorm_matmul_noalloc": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_float,
+         C.POINTER(Cfg), C.c_void_p, C.c_void_p],
+    ),
     "b200_rmsnorm_matmul_f32": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_float, C.c_void_p],

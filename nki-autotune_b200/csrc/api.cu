@@ -602,3 +602,58 @@ extern "C" int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg, void
   }
   return rc;
 }
+
+// =============================================================================== allocation-free entry
+// Some callers cannot hand the skinny kernel a workspace because they cannot allocate device
+// memory at the point of the call: a decode loop running inside a serving engine that has
+// already carved the whole device heap into its own pools, or a host thread that must not take
+// the allocator's locks.  For them the same kernel runs on a scratch that is part of this
+// library's device image: it costs NOALLOC_SCRATCH_BYTES on every GPU that loads the library,
+// for the life of the process, and it caps N at B200_NOALLOC_MAX_N.
+namespace b200 {
+constexpr size_t NOALLOC_SCRATCH_BYTES =
+    static_cast<size_t>(SKINNY_ROWS) * B200_NOALLOC_MAX_N * sizeof(float) + 4096;  // sums + tile counters
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+// Device address of the array, per device ordinal.  The symbol name above is only a host-side
+// handle: it must be turned into an address with cudaGetSymbolAddress while that device is current.
+static void* g_noalloc_addr[64] = {nullptr};
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, const void* w, void* out, long M,
+                                           long N, long K, float eps, const b200_cfg* cfg, int* dev_status,
+                                           void* stream_v) {
+  if (M <= 0 || M > SKINNY_ROWS)
+    return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul_noalloc: M=%ld, this entry point serves 1..%d rows", M,
+                     SKINNY_ROWS);
+  if (N <= 0 || N > B200_NOALLOC_MAX_N)
+    return set_error(B200_ERR_BAD_SHAPE,
+                     "rmsnorm_matmul_noalloc: N=%ld exceeds the built-in scratch (at most %d columns); use "
+                     "b200_rmsnorm_matmul with a caller-provided workspace",
+                     N, B200_NOALLOC_MAX_N);
+  const size_t need = skinny_workspace_bytes(N);
+  if (need > NOALLOC_SCRATCH_BYTES)
+    return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul_noalloc: N=%ld needs %zu scratch bytes, %zu are built in", N,
+                     need, NOALLOC_SCRATCH_BYTES);
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return set_error(B200_ERR_CUDA, "device ordinal %d out of range", dev);
+  if (g_noalloc_addr[dev] == nullptr) {
+    // first call on this device: resolve the address (do this before any stream capture)
+    void* addr = nullptr;
+    rc = check_cuda(cudaGetSymbolAddress(&addr, g_noalloc_scratch), "cudaGetSymbolAddress(built-in scratch)");
+    if (rc) return rc;
+    if (addr == nullptr) return set_error(B200_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_addr[dev] = addr;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  // The array keeps whatever the previous call (or an aborted one) left: the partial sums and the
+  // tile counters must start at zero, so the part this call uses is cleared on the same stream.
+  rc = check_cuda(cudaMemsetAsync(g_noalloc_addr[dev], 0, need, stream), "clearing the built-in scratch");
+  if (rc) return rc;
+  LaunchArgs la{FAM_RMSNORM, x, w, gamma, out, M, N, K, K, N, N, eps, g_noalloc_addr[dev], NOALLOC_SCRATCH_BYTES};
+  Prepared pr;
+  rc = prepare(la, cfg, dev_status, &pr);
+  if (rc) return rc;
+  return launch(pr, stream);
+}
