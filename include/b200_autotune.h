@@ -49,8 +49,13 @@ typedef struct b200_cfg {
   int cluster_m;  /* 1, or 2 = a CTA pair along M (tile_m 256: one 2-SM UMMA)               */
   int cluster_n;  /* 1 (reserved)                                                          */
   int swizzle;    /* tile rasterisation group width along M (1,2,4,8,16); 0 = default      */
-  int split_k;    /* skinny rmsnorm path only: K slices per output tile; 0 = automatic      */
-  int reserved[8];
+  int split_k;    /* reserved (the skinny kernel balances K ranges itself); 0               */
+  int norm_mode;  /* rmsnorm_matmul, M > 16: where the norm is applied.  1 = inline (x tiles are
+                     scaled on their way through tensor memory, no scratch), 2 = prologue (the
+                     launch first writes x*gamma and rinv to scratch, then runs the plain main
+                     loop; needs b200_workspace_bytes of scratch), 0 = prologue when a large
+                     enough workspace is passed, else inline                                */
+  int reserved[7];
 } b200_cfg;
 
 /* Number of ints in a dev_status block (device memory, caller-owned, zeroed by caller).
@@ -74,7 +79,8 @@ int b200_device_count(int* count);
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
                    long* smem_bytes, int* tmem_cols);
 
-/* Bytes of device scratch the candidate needs (0 for most). */
+/* Bytes of device scratch the candidate can use (0 when it needs none).  The scratch must be
+ * zero-filled once before first use; the kernels leave it reusable for the next launch. */
 size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K);
 
 /* C[M,N] (bf16, row stride ld_out) = lhsT[K,M]^T . rhs[K,N], bf16 operands, fp32

@@ -49,20 +49,23 @@ def raise_on_status(status: torch.Tensor) -> None:
         )
 
 
-_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+_WORKSPACES: dict[tuple, torch.Tensor] = {}
 
 
-def workspace_for(family: str, M: int, N: int, K: int, device) -> torch.Tensor | None:
-    """Zero-initialised device scratch for kernels that need it (``None`` when they do not).
+def workspace_for(family: str, M: int, N: int, K: int, device, cfg: dict | None = None) -> torch.Tensor | None:
+    """Device scratch for the kernels that use it (``None`` when they do not).
 
-    The skinny fused kernel keeps its scratch all-zero between launches, so one cached buffer
-    per (device, size) is reused; :func:`reset_workspaces` drops the cache after a failed launch.
+    The buffers are zero-filled once; the kernels leave them reusable (partial sums and
+    barrier counters back at zero), so one cached buffer per (device, kind, size) serves every
+    launch.  :func:`reset_workspaces` drops the cache after a failed launch.
     """
-    need = native.load().b200_workspace_bytes(family.encode(), None, M, N, K)
+    c = Cfg.from_dict(cfg)
+    need = native.load().b200_workspace_bytes(family.encode(), C.byref(c) if c is not None else None, M, N, K)
     if need == 0:
         return None
     dev = torch.device(device)
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(), int(need))
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    key = (index, "skinny" if M <= 16 else "prologue", int(need))
     buf = _WORKSPACES.get(key)
     if buf is None:
         buf = torch.zeros(int(need), dtype=torch.uint8, device=dev)
@@ -149,7 +152,7 @@ def rmsnorm_matmul(
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     c = Cfg.from_dict(cfg)
-    ws = workspace_for("rmsnorm_matmul", M, N, K, x.device)
+    ws = workspace_for("rmsnorm_matmul", M, N, K, x.device, cfg)
     native.check(
         lib.b200_rmsnorm_matmul(
             x.data_ptr(), gamma.data_ptr() if gamma is not None else None, weight.data_ptr(), out.data_ptr(),
@@ -207,7 +210,7 @@ def time_kernel(
     prob.eps = float(eps)
     ms = (C.c_float * iters)()
     c = Cfg.from_dict(cfg)
-    ws = workspace_for(family, M, N, K, a.device)
+    ws = workspace_for(family, M, N, K, a.device, cfg)
     native.check(
         lib.b200_time_kernel(
             C.byref(prob), C.byref(c) if c is not None else None,

@@ -18,13 +18,13 @@ ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_UNSUPPORTED, ERR_SMEM_OOM, ERR_TMEM_OOM = 1, 2, 
 ERR_CUDA, ERR_DEVICE_WAIT, ERR_WORKSPACE = 6, 7, 8
 DEV_STATUS_INTS = 8
 
-CFG_FIELDS = ("tile_m", "tile_n", "tile_k", "stages", "cluster_m", "cluster_n", "swizzle", "split_k")
+CFG_FIELDS = ("tile_m", "tile_n", "tile_k", "stages", "cluster_m", "cluster_n", "swizzle", "split_k", "norm_mode")
 
 
 class Cfg(C.Structure):
     """``b200_cfg``."""
 
-    _fields_ = [(name, C.c_int) for name in CFG_FIELDS] + [("reserved", C.c_int * 8)]
+    _fields_ = [(name, C.c_int) for name in CFG_FIELDS] + [("reserved", C.c_int * 7)]
 
     @classmethod
     def from_dict(cls, d: dict | None) -> "Cfg | None":

@@ -54,7 +54,8 @@ struct Plan {
   int a_col0, a_slots;  // fused kernel: tensor-memory ring that holds the scaled x tiles
   int a_stages, groups; // fused kernel: shared-memory ring of x tiles; transform warp groups
   long gamma_bytes;     // fused kernel: shared memory reserved for gamma
-  int skinny;           // fused kernel, M <= 16: the weight-streaming swap-AB kernel
+  int skinny;           // fused kernel, M <= 16: the weight-streaming kernel
+  int prologue;         // fused kernel, M > 16: prologue variant of the plain GEMM (needs scratch)
   long smem_bytes;
 };
 
@@ -107,6 +108,8 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
       return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul (skinny): need N %% 8 == 0 and K %% 64 == 0, got N=%ld K=%ld", N, K);
     return B200_OK;
   }
+  const bool prologue = (fam == FAM_RMSNORM && cfg.norm_mode == 2);
+  if (prologue) fam = FAM_LHST;  // same pipeline budgets as the plain GEMM
   const int cluster_m = cfg.cluster_m == 0 ? 1 : cfg.cluster_m;
   const int cluster_n = cfg.cluster_n == 0 ? 1 : cfg.cluster_n;
   if (cfg.tile_m != 128 && cfg.tile_m != 256)
@@ -117,6 +120,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     return set_error(B200_ERR_UNSUPPORTED, "cluster_n=%d: only 1 is implemented", cluster_n);
   Plan p;
   memset(&p, 0, sizeof(p));
+  p.prologue = prologue ? 1 : 0;
   p.cluster = cluster_m;
   p.tile_m = cfg.tile_m;
   if (cluster_m == 2 && cfg.tile_m == 256) { p.cta_group = 2; p.m_sub = 1; }
@@ -130,7 +134,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     return set_error(B200_ERR_UNSUPPORTED,
                      "tile_n=%d: need a multiple of %d in [64,256] (64-column operand chunks per CTA)",
                      cfg.tile_n, 64 * p.cta_group);
-  if (fam == FAM_RMSNORM ? (cfg.tile_k != 64 && cfg.tile_k != 128)
+  if ((fam == FAM_RMSNORM || prologue) ? (cfg.tile_k != 64 && cfg.tile_k != 128)
                          : (cfg.tile_k != 32 && cfg.tile_k != 64 && cfg.tile_k != 128))
     return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 are implemented", cfg.tile_k);
   if (cfg.stages < 1 || cfg.stages > MAX_STAGES)
@@ -153,7 +157,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     int slots = (512 - p.a_col0) / slot_cols;
     if (slots > MAX_A_SLOTS) slots = MAX_A_SLOTS;
     tmem_need = p.a_col0 + 2 * slot_cols;
-    p.gamma_bytes = ((K > 0 ? K : 0) * 2L + 15) & ~15L;
+    p.gamma_bytes = ((K > 0 ? K : 0) + 127) / 128 * 128 * 2L;  // whole k-blocks of either size
     ctrl_bytes = static_cast<long>(sizeof(RmsCtrl)) + p.gamma_bytes;
     // x ring: as deep as fits beside the w ring (8, 6, 4, 3, 2 or 1 stages).  The transform warp
     // groups take k-blocks round-robin, and both the x ring and the slot ring must be multiples
@@ -188,7 +192,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     if (M <= 0 || N <= 0 || K <= 0) return set_error(B200_ERR_BAD_SHAPE, "empty shape M=%ld N=%ld K=%ld", M, N, K);
     if (M % 8 != 0 || N % 8 != 0)
       return set_error(B200_ERR_BAD_SHAPE, "M=%ld and N=%ld must be multiples of 8 (16-byte rows)", M, N);
-    if (fam == FAM_RMSNORM && K % 64 != 0)
+    if ((fam == FAM_RMSNORM || prologue) && K % 64 != 0)
       return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul: K=%ld must be a multiple of 64", K);
     if (M > (1L << 30) || N > (1L << 30) || K > (1L << 30))
       return set_error(B200_ERR_BAD_SHAPE, "dimension beyond 2^30");
@@ -239,6 +243,11 @@ typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const GemmPar
 typedef void (*RmsKernelFn)(const CUtensorMap, const CUtensorMap, const RmsParams);
 
 static GemmKernelFn pick_gemm_kernel(const Plan& p) {
+  if (p.prologue) {
+    if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, true>;
+    if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, true>;
+    return gemm_tcgen05_kernel<1, 1, true>;
+  }
   if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1>;
   if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2>;
   return gemm_tcgen05_kernel<1, 1>;
@@ -287,6 +296,13 @@ struct LaunchArgs {
   void* workspace;
   size_t workspace_bytes;
 };
+
+static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+// prologue variant: [xg: M*K bf16][rinv: M fp32][grid barrier counters: 2 x u32]
+static size_t prologue_workspace_bytes(long M, long K) {
+  return align256(static_cast<size_t>(M) * K * 2) + align256(static_cast<size_t>(M) * sizeof(float)) + 256;
+}
 
 static size_t skinny_workspace_bytes(long N) {
   const size_t tiles = static_cast<size_t>((N + SKINNY_TILE_N - 1) / SKINNY_TILE_N);
@@ -360,6 +376,25 @@ static int prepare_skinny(const LaunchArgs& la, const b200_cfg* cfg, const Plan&
 
 static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, Prepared* pr) {
   if (!la.a || !la.b || !la.out) return set_error(B200_ERR_BAD_ARG, "NULL operand pointer");
+  // fused kernel, M > 16: choose where the norm is applied (b200_cfg.norm_mode)
+  b200_cfg eff;
+  if (la.fam == FAM_RMSNORM && la.M > SKINNY_ROWS) {
+    const int mode = cfg ? cfg->norm_mode : 0;
+    const bool have_ws = la.workspace != nullptr && la.workspace_bytes >= prologue_workspace_bytes(la.M, la.K);
+    if (mode < 0 || mode > 2) return set_error(B200_ERR_UNSUPPORTED, "norm_mode=%d: need 0, 1 or 2", mode);
+    if (mode == 2 && !have_ws)
+      return set_error(B200_ERR_WORKSPACE, "rmsnorm_matmul with norm_mode 2 needs %zu bytes of device workspace (got %zu)",
+                       prologue_workspace_bytes(la.M, la.K), la.workspace ? la.workspace_bytes : static_cast<size_t>(0));
+    if (mode == 2 || (mode == 0 && have_ws)) {
+      eff = cfg ? *cfg : default_cfg(FAM_LHST, la.M);
+      eff.norm_mode = 2;
+      cfg = &eff;
+    } else if (cfg != nullptr) {
+      eff = *cfg;
+      eff.norm_mode = 1;
+      cfg = &eff;
+    }
+  }
   Plan plan;
   int rc = make_plan(la.fam, cfg, la.M, la.N, la.K, &plan);
   if (rc) return rc;
@@ -374,7 +409,12 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
     return set_error(B200_ERR_BAD_ARG, "gamma: pointer must be 16-byte aligned");
 
   const int mc = 128 * plan.m_sub;
-  if (la.fam == FAM_LHST) {
+  uint8_t* ws = static_cast<uint8_t*>(la.workspace);
+  if (plan.prologue) {
+    if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0 || (reinterpret_cast<uintptr_t>(la.a) & 15u) != 0)
+      return set_error(B200_ERR_BAD_ARG, "workspace must be 256-byte aligned and x 16-byte aligned");
+    rc = make_tmap_bf16(&pr->tm_a, ws, la.M, la.K, la.K, 64, mc, "scaled x (workspace)");
+  } else if (la.fam == FAM_LHST) {
     rc = make_tmap_bf16(&pr->tm_a, la.a, la.K, la.M, la.ld_a, 64, plan.tile_k, "lhsT");
   } else {
     rc = make_tmap_bf16(&pr->tm_a, la.a, la.M, la.K, la.ld_a, 64, mc, "x");
@@ -404,8 +444,18 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (cfg && cfg->reserved[1] > 0) limit_us = cfg->reserved[1];
   gp.timeout_cycles = limit_us * (di.clock_khz > 0 ? di.clock_khz / 1000 : 1900);
   gp.debug_mode = cfg ? cfg->reserved[0] : 0;
+  if (plan.prologue) {
+    gp.x = static_cast<const __nv_bfloat16*>(la.a);
+    gp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
+    gp.xg = reinterpret_cast<__nv_bfloat16*>(ws);
+    gp.rinv = reinterpret_cast<float*>(ws + align256(static_cast<size_t>(la.M) * la.K * 2));
+    gp.grid_sync = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(gp.rinv) +
+                                                   align256(static_cast<size_t>(la.M) * sizeof(float)));
+    gp.eps = la.eps;
+    gp.inv_k = 1.0f / static_cast<float>(la.K);
+  }
 
-  const bool fused = (la.fam == FAM_RMSNORM);
+  const bool fused = (la.fam == FAM_RMSNORM) && !plan.prologue;
   RmsParams& rp = pr->rp;
   memset(&rp, 0, sizeof(rp));
   if (fused) {
@@ -523,9 +573,10 @@ extern "C" int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, l
 }
 
 extern "C" size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K) {
-  (void)cfg; (void)K;
-  if (parse_family(family) == FAM_RMSNORM && M > 0 && M <= SKINNY_ROWS && N > 0) return skinny_workspace_bytes(N);
-  return 0;
+  if (parse_family(family) != FAM_RMSNORM || M <= 0) return 0;
+  if (M <= SKINNY_ROWS) return N > 0 ? skinny_workspace_bytes(N) : 0;
+  if (cfg != nullptr && cfg->norm_mode == 1) return 0;  // inline norm needs no scratch
+  return K > 0 ? prologue_workspace_bytes(M, K) : 0;
 }
 
 extern "C" int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out, long M, long N, long K,

@@ -45,6 +45,13 @@ struct GemmParams {
   int* status;       // B200_DEV_STATUS_INTS ints or nullptr
   long long timeout_cycles;
   int debug_mode;    // 0, or one of the DEBUG_* hooks
+  // NORM variant only (fused RMSNorm with an in-kernel prologue):
+  const __nv_bfloat16* x;      // [M,K] activations
+  const __nv_bfloat16* gamma;  // [K] or nullptr
+  __nv_bfloat16* xg;           // scratch [M,K]: x * gamma, the K-major A operand of the main loop
+  float* rinv;                 // scratch [M]: rsqrt(mean_k x^2 + eps)
+  unsigned int* grid_sync;     // scratch [2]: arrive / depart counters, zero between launches
+  float eps, inv_k;
 };
 
 // Control block that follows the operand stages in dynamic shared memory.
@@ -114,7 +121,15 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int gro
   nt = r / gsize;
 }
 
-template <int CTA_GROUP, int M_SUB>
+// NORM = false: C = lhsT^T . rhs (A MN-major from lhsT[K,M]).
+// NORM = true : out = (x / rms(x) * gamma) . w in one launch with a prologue: every CTA first
+//   scales its share of the rows of x by gamma into the scratch xg and stores rinv[m]; after a
+//   grid-wide barrier (all CTAs are resident: the grid never exceeds what fits the machine) the
+//   same main loop runs with A = xg (K-major) and the epilogue multiplies row m by rinv[m].
+//   x is read once; xg costs one extra write and read of M*K*2 bytes, hidden under the tensor
+//   work.  (kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 is the two-pass form of the
+//   same maths.)
+template <int CTA_GROUP, int M_SUB, bool NORM = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
@@ -176,8 +191,83 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   WaitCtx wctx{ctrl, p.status, p.timeout_cycles, 0};
 
+  if constexpr (NORM) {
+    // ---------------------------------------------------------------- prologue: xg, rinv
+    const int warps_total = static_cast<int>(gridDim.x) * (GEMM_THREADS / 32);
+    const int pieces = p.K / 8;  // 16-byte pieces per row (K is a multiple of 64)
+    for (int row = static_cast<int>(blockIdx.x) * (GEMM_THREADS / 32) + warp; row < p.M; row += warps_total) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K);
+      uint4* dst = reinterpret_cast<uint4*>(p.xg + static_cast<long long>(row) * p.K);
+      float ss = 0.0f, ss2 = 0.0f;
+      for (int i0 = lane; i0 < pieces; i0 += 128) {  // four independent pieces in flight per lane
+        uint4 v[4], g[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 32;
+          v[u] = (i < pieces) ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+          g[u] = (i < pieces && p.gamma != nullptr) ? __ldg(reinterpret_cast<const uint4*>(p.gamma) + i)
+                                                    : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * 32;
+          const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
+            ss = fmaf(lo, lo, ss);
+            ss2 = fmaf(hi, hi, ss2);
+          }
+          if (i < pieces)
+            dst[i] = make_uint4(mul_bf16x2(v[u].x, g[u].x), mul_bf16x2(v[u].y, g[u].y), mul_bf16x2(v[u].z, g[u].z),
+                                mul_bf16x2(v[u].w, g[u].w));
+        }
+      }
+      ss += ss2;
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      if (lane == 0) p.rinv[row] = rsqrtf(ss * p.inv_k + p.eps);
+    }
+    // ---------------------------------------------------------------- grid-wide barrier (bounded)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      atomicAdd(p.grid_sync, 1u);
+      const long long t0 = clock64();
+      bool arrived = true;
+      while (*reinterpret_cast<volatile unsigned int*>(p.grid_sync) < gridDim.x) {
+        if (clock64() - t0 > p.timeout_cycles) {
+          arrived = false;
+          break;
+        }
+        __nanosleep(200);
+      }
+      if (arrived) {
+        __threadfence();
+        // the last CTA to leave puts both counters back to zero for the next launch
+        if (atomicAdd(p.grid_sync + 1, 1u) == gridDim.x - 1) {
+          p.grid_sync[0] = 0u;
+          p.grid_sync[1] = 0u;
+          __threadfence();
+        }
+      } else {
+        ctrl->abort_flag = 1;
+        if (p.status != nullptr && atomicCAS(p.status, 0, 7) == 0) {
+          p.status[1] = 5;  // grid barrier
+          p.status[5] = static_cast<int>(blockIdx.x);
+        }
+      }
+    }
+    __syncthreads();
+    // order the other CTAs' generic-proxy stores to xg before this CTA's TMA (async proxy) loads
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
+  const bool run_roles = !NORM || ctrl->abort_flag == 0;
+
   // ------------------------------------------------------------------ TMA producer
-  if (warp == 0) {
+  if (!run_roles) {
+    // a CTA that gave up at the grid barrier skips straight to the teardown
+  } else if (warp == 0) {
     if (lane == 0 && p.debug_mode != DEBUG_SKIP_PRODUCER) {
       wctx.role = ROLE_PRODUCER;
       uint32_t it = 0;
@@ -203,14 +293,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           } else if constexpr (PAIR) {
             const uint32_t full_leader = map_to_cta(full_local, 0);
             if (cta_rank == 0) mbar_arrive_expect_tx(full_local, 2u * (a_bytes + b_bytes));
-            for (int c = 0; c < MC / 64; ++c)
-              tma_load_2d_pair(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
+            if constexpr (NORM) {
+              for (int c = 0; c < tile_k / 64; ++c)
+                tma_load_2d_pair(a_s + c * MC * 128, &tm_a, full_leader, k0 + 64 * c, m_base);
+            } else {
+              for (int c = 0; c < MC / 64; ++c)
+                tma_load_2d_pair(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
+            }
             for (int c = 0; c < nc / 64; ++c)
               tma_load_2d_pair(b_s + c * tile_k * 128, &tm_b, full_leader, n_base + 64 * c, k0);
           } else {
             mbar_arrive_expect_tx(full_local, a_bytes + b_bytes);
-            for (int c = 0; c < MC / 64; ++c)
-              tma_load_2d(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
+            if constexpr (NORM) {
+              for (int c = 0; c < tile_k / 64; ++c)
+                tma_load_2d(a_s + c * MC * 128, &tm_a, full_local, k0 + 64 * c, m_base);
+            } else {
+              for (int c = 0; c < MC / 64; ++c)
+                tma_load_2d(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
+            }
             for (int c = 0; c < nc / 64; ++c)
               tma_load_2d(b_s + c * tile_k * 128, &tm_b, full_local, n_base + 64 * c, k0);
           }
@@ -228,7 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (lane == 0 && cta_rank == 0) {
       wctx.role = ROLE_MMA;
       const uint32_t idesc =
-          make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, 1, 1);
+          make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, NORM ? 0 : 1, 1);
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
       // descriptors: the high word (stride offset, version, swizzle) and the leading offset are
       // fixed; only the 14-bit start-address field moves (16-byte units: 128 per 16 k-rows)
@@ -256,9 +356,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll 4
             for (int k16 = 0; k16 < nk16; ++k16, adesc += 128, bdesc += 128) {
 #pragma unroll
-              for (int mi = 0; mi < M_SUB; ++mi)
-                umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n), adesc + mi * sub_step, bdesc,
-                                     idesc, (kb | k16) != 0 ? 1u : 0u);
+              for (int mi = 0; mi < M_SUB; ++mi) {
+                uint64_t ad = adesc + mi * sub_step;
+                if constexpr (NORM)  // K-major x tile: 64-wide k chunks of MC rows x 128 B, 32 B per 16 k
+                  ad = make_smem_desc_sw128(a_base + s * a_bytes + (k16 >> 2) * (MC * 128) + mi * (128 * 128) +
+                                                (k16 & 3) * 32, 16, 1024);
+                umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n), ad, bdesc, idesc,
+                                     (kb | k16) != 0 ? 1u : 0u);
+              }
             }
           }
           if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->empty[s]), 3);
@@ -295,6 +400,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       for (int mi = 0; mi < M_SUB; ++mi) {
         const long long grow = static_cast<long long>(m_base) + mi * 128 + row_in_cta;
         __nv_bfloat16* out_row = p.out + grow * p.ld_out;
+        float scale = 1.0f;
+        if constexpr (NORM) scale = (grow < p.M) ? __ldcg(p.rinv + grow) : 0.0f;
         for (int c = 0; c < tile_n / 32; ++c) {
           uint32_t r[32];
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
@@ -308,14 +415,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               const int col = col0 + g * 8;
               if (col + 8 <= p.N) {
                 uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]),
-                                  __uint_as_float(r[g * 8 + 1]));
-                v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]),
-                                  __uint_as_float(r[g * 8 + 3]));
-                v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]),
-                                  __uint_as_float(r[g * 8 + 5]));
-                v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]),
-                                  __uint_as_float(r[g * 8 + 7]));
+                v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * scale, __uint_as_float(r[g * 8 + 1]) * scale);
+                v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * scale, __uint_as_float(r[g * 8 + 3]) * scale);
+                v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * scale, __uint_as_float(r[g * 8 + 5]) * scale);
+                v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * scale, __uint_as_float(r[g * 8 + 7]) * scale);
                 *reinterpret_cast<uint4*>(out_row + col) = v;
               }
             }

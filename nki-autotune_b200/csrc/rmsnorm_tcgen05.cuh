@@ -178,7 +178,10 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
   if (p.gamma_bytes > 0) {
     const uint4* src = reinterpret_cast<const uint4*>(p.gamma);
     uint4* dst = reinterpret_cast<uint4*>(smem_gen + gamma_addr);
-    for (int i = threadIdx.x; i < p.gamma_bytes / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+    // staged length is K rounded up to whole k-blocks; the tail is zero so that it multiplies the
+    // zero-filled x columns beyond K into zeros (never garbage)
+    for (int i = threadIdx.x; i < p.gamma_bytes / 16; i += blockDim.x)
+      dst[i] = (i * 8 < p.K) ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
   }
   tc_fence_before();
   __syncthreads();

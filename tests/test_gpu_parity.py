@@ -22,8 +22,8 @@ def N_(k):
     return {"kind": "normal", "scale": k ** -0.5}
 
 
-def cfg(tm, tn, tk, st, cm=1, sw=0):
-    return dict(tile_m=tm, tile_n=tn, tile_k=tk, stages=st, cluster_m=cm, swizzle=sw)
+def cfg(tm, tn, tk, st, cm=1, sw=0, nm=0):
+    return dict(tile_m=tm, tile_n=tn, tile_k=tk, stages=st, cluster_m=cm, swizzle=sw, norm_mode=nm)
 
 
 @pytest.fixture(scope="module")
@@ -161,6 +161,38 @@ def test_rmsnorm_golden_cases(K, golden, key, seed, m, k, n, eps, c):
     assert O.max_abs_rel_err(got, expect) <= TOL_BF16
 
 
+@pytest.mark.parametrize("nm", [1, 2], ids=["inline", "prologue"])
+@pytest.mark.parametrize("m,k,n", [(256, 512, 384), (1000, 512, 1016), (2048, 2048, 2048), (136, 64, 72)])
+@pytest.mark.parametrize("tiles", [(128, 128, 64, 3, 1), (128, 256, 128, 2, 1), (256, 256, 64, 4, 2), (256, 256, 128, 3, 2),
+                                   (256, 128, 64, 3, 1)], ids=["1cta", "1cta-k128", "pair", "pair-k128", "msub2"])
+def test_rmsnorm_both_norm_placements(K, nm, m, k, n, tiles):
+    """Inline (tensor-memory path) and prologue (same-launch scratch) variants, twice in a row."""
+    tm, tn, tk, st, cm = tiles
+    for _ in range(2):
+        got, expect = _rms_case(K, 23, m, k, n, 1e-6, cfg(tm, tn, tk, st, cm=cm, nm=nm))
+        assert O.max_abs_rel_err(got, expect) <= TOL_BF16
+
+
+def test_rmsnorm_prologue_needs_workspace(K):
+    import torch
+
+    from autotune import native
+
+    lib = native.load()
+    x = torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda")
+    c = native.Cfg.from_dict(cfg(128, 128, 64, 3, nm=2))
+    import ctypes as C
+
+    rc = lib.b200_rmsnorm_matmul(x.data_ptr(), None, w.data_ptr(), out.data_ptr(), 128, 256, 256, 1e-6, C.byref(c), None, 0,
+                                 None, torch.cuda.current_stream().cuda_stream)
+    assert rc == native.ERR_WORKSPACE
+    c1 = native.Cfg.from_dict(cfg(128, 128, 64, 3, nm=1))
+    assert lib.b200_workspace_bytes(b"rmsnorm_matmul", C.byref(c1), 128, 256, 256) == 0
+    assert lib.b200_workspace_bytes(b"rmsnorm_matmul", C.byref(c), 128, 256, 256) >= 128 * 256 * 2 + 128 * 4
+
+
 def test_rmsnorm_without_gamma_is_reference_kernel_maths(K, golden):
     t = O.generate_inputs(0, [("lhs", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
     got = K.rmsnorm_matmul_host(t["lhs"].astype(BF), None, t["rhs"].astype(BF), 1e-6).astype(np.float32)
@@ -223,7 +255,7 @@ def test_rmsnorm_skinny_without_workspace_is_an_error(K):
                                  torch.cuda.current_stream().cuda_stream)
     assert rc == native.ERR_WORKSPACE and "workspace" in native.last_error()
     assert lib.b200_workspace_bytes(b"rmsnorm_matmul", None, 16, 256, 256) >= 16 * 256 * 4
-    assert lib.b200_workspace_bytes(b"rmsnorm_matmul", None, 4096, 256, 256) == 0
+    assert lib.b200_workspace_bytes(b"matmul_lhsT_rhs", None, 4096, 256, 256) == 0
 
 
 # ---- argument checking and bounded waits -------------------------------------------------------
