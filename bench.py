@@ -213,12 +213,25 @@ def timed_region(ranks: Ranks, torch, body, steps: int) -> float:
     return ranks.max(e0.elapsed_time(e1) / steps)
 
 
+def use_all_host_threads() -> int:
+    """Let the BLAS behind numpy use every host core (torchrun exports OMP_NUM_THREADS=1)."""
+    n = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=n)
+    except Exception:  # noqa: BLE001 - best effort; the core count reported stays what was asked for
+        pass
+    return n
+
+
 def cpu_baseline_sample(lhs_T_bf16, rhs_bf16, sample_cols: int) -> tuple[float, float, "object"]:
     """Times the CPU oracle on lhsT[:, :sample_cols] (a row block of C); returns (s, TFLOP/s, C block)."""
     import numpy as np
 
     from oracle import oracle as O
 
+    use_all_host_threads()
     a = np.ascontiguousarray(lhs_T_bf16[:, :sample_cols]).astype(np.float32)
     b = rhs_bf16.astype(np.float32)
     O.matmul_lhsT_rhs(a[:, :256], b)  # warm the BLAS threads
@@ -459,6 +472,7 @@ def run_reference(args) -> None:
     from oracle import oracle as O
 
     sample = 2048  # columns of lhsT = rows of C per step: a quarter of the 8192^3 workload
+    use_all_host_threads()
     lhs_T_np, rhs_np = make_inputs()
     a = np.ascontiguousarray(lhs_T_np[:, :sample]).astype(np.float32)
     b = rhs_np.astype(np.float32)

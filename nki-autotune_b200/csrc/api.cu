@@ -135,8 +135,8 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
                      "tile_n=%d: need a multiple of %d in [64,256] (64-column operand chunks per CTA)",
                      cfg.tile_n, 64 * p.cta_group);
   if ((fam == FAM_RMSNORM || prologue) ? (cfg.tile_k != 64 && cfg.tile_k != 128)
-                         : (cfg.tile_k != 32 && cfg.tile_k != 64 && cfg.tile_k != 128))
-    return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 are implemented", cfg.tile_k);
+                         : (cfg.tile_k != 32 && cfg.tile_k != 64 && cfg.tile_k != 96 && cfg.tile_k != 128))
+    return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 (plain GEMM also 32 and 96) are implemented", cfg.tile_k);
   if (cfg.stages < 1 || cfg.stages > MAX_STAGES)
     return set_error(B200_ERR_UNSUPPORTED, "stages=%d: need 1..%d", cfg.stages, MAX_STAGES);
   if (cfg.swizzle < 0 || cfg.swizzle > 64)
