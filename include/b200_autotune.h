@@ -73,7 +73,7 @@ int b200_device_count(int* count);
 /* Candidate validation without touching the GPU: computes the shared-memory bytes and
  * tensor-memory columns the candidate needs and returns B200_ERR_SMEM_OOM /
  * B200_ERR_TMEM_OOM / B200_ERR_UNSUPPORTED / B200_ERR_BAD_SHAPE when it cannot run.
- * family is "matmul_lhsT_rhs" or "rmsnorm_matmul".
+ * family is "matmul_lhsT_rhs", "matmul_lhs_rhs" or "rmsnorm_matmul".
  * Stands in for the compile step, compile_one(), autotune/src/autotune/runner/compile.py:197-244:
  * an over-subscribed candidate is a reported failure, never silently dropped. */
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
@@ -92,6 +92,14 @@ int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out,
                          long M, long N, long K, long ld_lhsT, long ld_rhs, long ld_out,
                          const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
                          int* dev_status, void* stream);
+
+/* C[M,N] (bf16) = lhs[M,K] . rhs[K,N] with lhs K-contiguous (row stride ld_lhs): the same
+ * kernel with a K-major A operand; no transpose pass is needed on this hardware.
+ * Replaces matmul_lhs_rhs_nkigym, kernel_library/matmul/lhs_rhs/kernel_handtuned_89.26mfu.py:226-287. */
+int b200_matmul_lhs_rhs(const void* lhs, const void* rhs, void* out,
+                        long M, long N, long K, long ld_lhs, long ld_rhs, long ld_out,
+                        const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
+                        int* dev_status, void* stream);
 
 /* Same contraction in fp32 on the CUDA cores (no tensor cores, no tf32): the 1e-5
  * configuration and the on-device cross-check for the tensor-core candidates.
@@ -142,8 +150,8 @@ int b200_rmsnorm_matmul_f32(const void* x, const void* gamma, const void* w, voi
  * Stands in for benchmark_one() + extract_perf_metrics,
  * autotune/src/autotune/runner/benchmark.py:116-153 and :58-87. */
 typedef struct b200_problem {
-  const char* family;          /* "matmul_lhsT_rhs" | "rmsnorm_matmul"                      */
-  const void* a;               /* lhsT[K,M] or x[M,K]                                      */
+  const char* family;          /* "matmul_lhsT_rhs" | "matmul_lhs_rhs" | "rmsnorm_matmul"   */
+  const void* a;               /* lhsT[K,M], lhs[M,K] or x[M,K]                            */
   const void* b;               /* rhs[K,N]  or w[K,N]                                      */
   const void* gamma;           /* rmsnorm only, may be NULL                                */
   void* out;

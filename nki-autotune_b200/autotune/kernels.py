@@ -129,6 +129,36 @@ def matmul_lhsT_rhs(
     return out
 
 
+def matmul_lhs_rhs(
+    lhs: torch.Tensor,
+    rhs: torch.Tensor,
+    cfg: dict | None = None,
+    out: torch.Tensor | None = None,
+    status: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``lhs @ rhs`` for bf16 ``lhs[M, K]`` (K contiguous) and ``rhs[K, N]``: replaces
+    ``matmul_lhs_rhs_nkigym`` (``kernel_library/matmul/lhs_rhs/kernel_handtuned_89.26mfu.py:226-287``)."""
+    _require_cuda(lhs, rhs)
+    lib = native.load()
+    M, K = lhs.shape
+    K2, N = rhs.shape
+    if K != K2:
+        raise NativeError(native.ERR_BAD_SHAPE, f"contraction mismatch: lhs has K={K}, rhs has K={K2}")
+    if lhs.dtype != torch.bfloat16 or rhs.dtype != torch.bfloat16:
+        raise NativeError(native.ERR_BAD_ARG, "matmul_lhs_rhs: bf16 operands only")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=lhs.device)
+    c = Cfg.from_dict(cfg)
+    native.check(
+        lib.b200_matmul_lhs_rhs(
+            lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(), M, N, K, _ld(lhs), _ld(rhs), _ld(out),
+            C.byref(c) if c is not None else None, None, 0,
+            status.data_ptr() if status is not None else None, _stream_ptr(),
+        )
+    )
+    return out
+
+
 def rmsnorm_matmul(
     x: torch.Tensor,
     gamma: torch.Tensor | None,

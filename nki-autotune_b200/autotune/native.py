@@ -88,6 +88,11 @@ SIGNATURES = {
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_long, C.c_long, C.c_long,
          C.POINTER(Cfg), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p],
     ),
+    "b200_matmul_lhs_rhs": (
+        C.c_int,
+        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_long, C.c_long, C.c_long,
+         C.POINTER(Cfg), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p],
+    ),
     "b200_matmul_lhsT_rhs_f32": (
         C.c_int,
         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_long, C.c_long, C.c_long, C.c_long, C.c_long, C.c_void_p],

@@ -53,7 +53,7 @@ def generate_tensors(tensor_specs: dict[str, dict], seed: int) -> dict[str, np.n
 def algorithmic_work(family: str, M: int, N: int, K: int, elem_bytes: int) -> tuple[float, float]:
     """(FLOPs, compulsory bytes): every operand read once, the output written once."""
     flops = 2.0 * M * N * K
-    if family == "matmul_lhsT_rhs":
+    if family in ("matmul_lhsT_rhs", "matmul_lhs_rhs"):
         nbytes = (K * M + K * N + M * N) * elem_bytes
     else:
         nbytes = (M * K + K * N + M * N + K) * elem_bytes
@@ -108,6 +108,8 @@ class DeviceBatch:
 
         if self.family == "matmul_lhsT_rhs":
             ref = kernels.matmul_lhsT_rhs(self.a.float(), self.b.float())
+        elif self.family == "matmul_lhs_rhs":
+            ref = kernels.matmul_lhsT_rhs(self.a.float().t().contiguous(), self.b.float())
         else:
             ref = kernels.rmsnorm_matmul_f32(self.a, self.gamma, self.b, float(self.scalars.get("eps", 1e-6)))
         torch.cuda.synchronize()

@@ -16,7 +16,7 @@ from dataclasses import dataclass, field
 
 from autotune.runner.types import KernelJob
 
-FAMILIES = ("matmul_lhsT_rhs", "rmsnorm_matmul")
+FAMILIES = ("matmul_lhsT_rhs", "matmul_lhs_rhs", "rmsnorm_matmul")
 CONFIG_KEYS = ("tile_m", "tile_n", "tile_k", "stages", "cluster_m", "cluster_n", "swizzle", "split_k", "norm_mode")
 
 

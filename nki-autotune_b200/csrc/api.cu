@@ -36,12 +36,13 @@ int check_cuda(cudaError_t e, const char* what) {
 // ---------------------------------------------------------------------------- plan
 constexpr long SMEM_BUDGET = 232448;  // 227 KB: largest opt-in dynamic shared memory per CTA
 
-enum Family { FAM_LHST = 0, FAM_RMSNORM = 1, FAM_UNKNOWN = -1 };
+enum Family { FAM_LHST = 0, FAM_RMSNORM = 1, FAM_LHS = 2, FAM_UNKNOWN = -1 };
 
 static Family parse_family(const char* family) {
   if (family == nullptr) return FAM_UNKNOWN;
   if (strcmp(family, "matmul_lhsT_rhs") == 0) return FAM_LHST;
   if (strcmp(family, "rmsnorm_matmul") == 0) return FAM_RMSNORM;
+  if (strcmp(family, "matmul_lhs_rhs") == 0) return FAM_LHS;
   return FAM_UNKNOWN;
 }
 
@@ -56,6 +57,7 @@ struct Plan {
   long gamma_bytes;     // fused kernel: shared memory reserved for gamma
   int skinny;           // fused kernel, M <= 16: the weight-streaming kernel
   int prologue;         // fused kernel, M > 16: prologue variant of the plain GEMM (needs scratch)
+  int a_kmajor;         // matmul_lhs_rhs: A is [M,K] with K contiguous
   long smem_bytes;
 };
 
@@ -83,7 +85,7 @@ static int next_pow2_cols(int cols) {
 // Validates a candidate and derives the launch plan.  Shape checks are skipped when M == 0.
 static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K, Plan* plan) {
   if (fam == FAM_UNKNOWN)
-    return set_error(B200_ERR_BAD_ARG, "unknown kernel family (expected matmul_lhsT_rhs or rmsnorm_matmul)");
+    return set_error(B200_ERR_BAD_ARG, "unknown kernel family (expected matmul_lhsT_rhs, matmul_lhs_rhs or rmsnorm_matmul)");
   b200_cfg cfg = cfg_in ? *cfg_in : default_cfg(fam, M);
   if (fam == FAM_RMSNORM && M > 0 && M <= SKINNY_ROWS) {
     // skinny activations: the weight-streaming kernel; only tile_k and stages apply
@@ -109,7 +111,8 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     return B200_OK;
   }
   const bool prologue = (fam == FAM_RMSNORM && cfg.norm_mode == 2);
-  if (prologue) fam = FAM_LHST;  // same pipeline budgets as the plain GEMM
+  const bool lhs_kmajor = (fam == FAM_LHS);
+  if (prologue || lhs_kmajor) fam = FAM_LHST;  // same pipeline budgets as the plain GEMM
   const int cluster_m = cfg.cluster_m == 0 ? 1 : cfg.cluster_m;
   const int cluster_n = cfg.cluster_n == 0 ? 1 : cfg.cluster_n;
   if (cfg.tile_m != 128 && cfg.tile_m != 256)
@@ -121,6 +124,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
   Plan p;
   memset(&p, 0, sizeof(p));
   p.prologue = prologue ? 1 : 0;
+  p.a_kmajor = lhs_kmajor ? 1 : 0;
   p.cluster = cluster_m;
   p.tile_m = cfg.tile_m;
   if (cluster_m == 2 && cfg.tile_m == 256) { p.cta_group = 2; p.m_sub = 1; }
@@ -134,7 +138,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     return set_error(B200_ERR_UNSUPPORTED,
                      "tile_n=%d: need a multiple of %d in [64,256] (64-column operand chunks per CTA)",
                      cfg.tile_n, 64 * p.cta_group);
-  if ((fam == FAM_RMSNORM || prologue) ? (cfg.tile_k != 64 && cfg.tile_k != 128)
+  if ((fam == FAM_RMSNORM || prologue || lhs_kmajor) ? (cfg.tile_k != 64 && cfg.tile_k != 128)
                          : (cfg.tile_k != 32 && cfg.tile_k != 64 && cfg.tile_k != 96 && cfg.tile_k != 128))
     return set_error(B200_ERR_UNSUPPORTED, "tile_k=%d: only 64 and 128 (plain GEMM also 32 and 96) are implemented", cfg.tile_k);
   if (cfg.stages < 1 || cfg.stages > MAX_STAGES)
@@ -194,6 +198,8 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
       return set_error(B200_ERR_BAD_SHAPE, "M=%ld and N=%ld must be multiples of 8 (16-byte rows)", M, N);
     if ((fam == FAM_RMSNORM || prologue) && K % 64 != 0)
       return set_error(B200_ERR_BAD_SHAPE, "rmsnorm_matmul: K=%ld must be a multiple of 64", K);
+    if (lhs_kmajor && K % 8 != 0)
+      return set_error(B200_ERR_BAD_SHAPE, "matmul_lhs_rhs: K=%ld must be a multiple of 8 (16-byte rows of lhs)", K);
     if (M > (1L << 30) || N > (1L << 30) || K > (1L << 30))
       return set_error(B200_ERR_BAD_SHAPE, "dimension beyond 2^30");
   }
@@ -244,9 +250,14 @@ typedef void (*RmsKernelFn)(const CUtensorMap, const CUtensorMap, const RmsParam
 
 static GemmKernelFn pick_gemm_kernel(const Plan& p) {
   if (p.prologue) {
-    if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, true>;
-    if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, true>;
-    return gemm_tcgen05_kernel<1, 1, true>;
+    if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, A_NORM>;
+    if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, A_NORM>;
+    return gemm_tcgen05_kernel<1, 1, A_NORM>;
+  }
+  if (p.a_kmajor) {
+    if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, A_KMAJOR_PLAIN>;
+    if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, A_KMAJOR_PLAIN>;
+    return gemm_tcgen05_kernel<1, 1, A_KMAJOR_PLAIN>;
   }
   if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1>;
   if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2>;
@@ -414,13 +425,15 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
     if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0 || (reinterpret_cast<uintptr_t>(la.a) & 15u) != 0)
       return set_error(B200_ERR_BAD_ARG, "workspace must be 256-byte aligned and x 16-byte aligned");
     rc = make_tmap_bf16(&pr->tm_a, ws, la.M, la.K, la.K, 64, mc, "scaled x (workspace)");
+  } else if (la.fam == FAM_LHS) {
+    rc = make_tmap_bf16(&pr->tm_a, la.a, la.M, la.K, la.ld_a, 64, mc, "lhs");
   } else if (la.fam == FAM_LHST) {
     rc = make_tmap_bf16(&pr->tm_a, la.a, la.K, la.M, la.ld_a, 64, plan.tile_k, "lhsT");
   } else {
     rc = make_tmap_bf16(&pr->tm_a, la.a, la.M, la.K, la.ld_a, 64, mc, "x");
   }
   if (rc) return rc;
-  rc = make_tmap_bf16(&pr->tm_b, la.b, la.K, la.N, la.ld_b, 64, plan.tile_k, la.fam == FAM_LHST ? "rhs" : "w");
+  rc = make_tmap_bf16(&pr->tm_b, la.b, la.K, la.N, la.ld_b, 64, plan.tile_k, la.fam == FAM_RMSNORM ? "w" : "rhs");
   if (rc) return rc;
 
   GemmParams& gp = pr->gp;
@@ -590,6 +603,17 @@ extern "C" int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out
   return launch(pr, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int b200_matmul_lhs_rhs(const void* lhs, const void* rhs, void* out, long M, long N, long K, long ld_lhs,
+                                   long ld_rhs, long ld_out, const b200_cfg* cfg, void* workspace,
+                                   size_t workspace_bytes, int* dev_status, void* stream) {
+  LaunchArgs la{FAM_LHS, lhs, rhs, nullptr, out, M, N, K, ld_lhs ? ld_lhs : K, ld_rhs ? ld_rhs : N,
+                ld_out ? ld_out : N, 0.0f, workspace, workspace_bytes};
+  Prepared pr;
+  int rc = prepare(la, cfg, dev_status, &pr);
+  if (rc) return rc;
+  return launch(pr, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out, long M, long N,
                                    long K, float eps, const b200_cfg* cfg, void* workspace, size_t workspace_bytes,
                                    int* dev_status, void* stream) {
@@ -613,7 +637,7 @@ extern "C" int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg, void
   la.M = p->M; la.N = p->N; la.K = p->K;
   if (fam == FAM_LHST) {
     la.ld_a = p->ld_a ? p->ld_a : p->M;
-  } else {
+  } else {  // x[M,K] and lhs[M,K]: K contiguous
     la.ld_a = p->ld_a ? p->ld_a : p->K;
   }
   la.ld_b = p->ld_b ? p->ld_b : p->N;

@@ -121,18 +121,26 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int gro
   nt = r / gsize;
 }
 
-// NORM = false: C = lhsT^T . rhs (A MN-major from lhsT[K,M]).
-// NORM = true : out = (x / rms(x) * gamma) . w in one launch with a prologue: every CTA first
+// A_MODE 0: C = lhsT^T . rhs (A MN-major from lhsT[K,M]).
+// A_MODE 1 (NORM): out = (x / rms(x) * gamma) . w in one launch with a prologue: every CTA first
 //   scales its share of the rows of x by gamma into the scratch xg and stores rinv[m]; after a
 //   grid-wide barrier (all CTAs are resident: the grid never exceeds what fits the machine) the
 //   same main loop runs with A = xg (K-major) and the epilogue multiplies row m by rinv[m].
 //   x is read once; xg costs one extra write and read of M*K*2 bytes, hidden under the tensor
 //   work.  (kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 is the two-pass form of the
 //   same maths.)
-template <int CTA_GROUP, int M_SUB, bool NORM = false>
+// A_MODE 2: C = lhs . rhs with lhs[M,K] K-major (matmul_lhs_rhs): the K-major operand path of
+//   the NORM variant without prologue or row scale.  The reference needs a DMA-transpose pass
+//   for this layout (kernel_library/matmul/lhs_rhs/kernel_handtuned_89.26mfu.py:226-287); the
+//   UMMA takes it directly.
+constexpr int A_LHST = 0, A_NORM = 1, A_KMAJOR_PLAIN = 2;
+
+template <int CTA_GROUP, int M_SUB, int A_MODE = A_LHST>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                     const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+  constexpr bool NORM = (A_MODE == A_NORM);
+  constexpr bool A_KMAJOR = (A_MODE != A_LHST);
   constexpr bool PAIR = (CTA_GROUP == 2);
   constexpr int MC = 128 * M_SUB;  // accumulator rows held by this CTA
   extern __shared__ uint8_t smem_raw[];
@@ -293,7 +301,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           } else if constexpr (PAIR) {
             const uint32_t full_leader = map_to_cta(full_local, 0);
             if (cta_rank == 0) mbar_arrive_expect_tx(full_local, 2u * (a_bytes + b_bytes));
-            if constexpr (NORM) {
+            if constexpr (A_KMAJOR) {
               for (int c = 0; c < tile_k / 64; ++c)
                 tma_load_2d_pair(a_s + c * MC * 128, &tm_a, full_leader, k0 + 64 * c, m_base);
             } else {
@@ -304,7 +312,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               tma_load_2d_pair(b_s + c * tile_k * 128, &tm_b, full_leader, n_base + 64 * c, k0);
           } else {
             mbar_arrive_expect_tx(full_local, a_bytes + b_bytes);
-            if constexpr (NORM) {
+            if constexpr (A_KMAJOR) {
               for (int c = 0; c < tile_k / 64; ++c)
                 tma_load_2d(a_s + c * MC * 128, &tm_a, full_local, k0 + 64 * c, m_base);
             } else {
@@ -328,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (lane == 0 && cta_rank == 0) {
       wctx.role = ROLE_MMA;
       const uint32_t idesc =
-          make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, NORM ? 0 : 1, 1);
+          make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, A_KMAJOR ? 0 : 1, 1);
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
       // descriptors: the high word (stride offset, version, swizzle) and the leading offset are
       // fixed; only the 14-bit start-address field moves (16-byte units: 128 per 16 k-rows)
@@ -358,7 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
               for (int mi = 0; mi < M_SUB; ++mi) {
                 uint64_t ad = adesc + mi * sub_step;
-                if constexpr (NORM)  // K-major x tile: 64-wide k chunks of MC rows x 128 B, 32 B per 16 k
+                if constexpr (A_KMAJOR)  // K-major x tile: 64-wide k chunks of MC rows x 128 B, 32 B per 16 k
                   ad = make_smem_desc_sw128(a_base + s * a_bytes + (k16 >> 2) * (MC * 128) + mi * (128 * 128) +
                                                 (k16 & 3) * 32, 16, 1024);
                 umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n), ad, bdesc, idesc,

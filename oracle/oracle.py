@@ -62,6 +62,13 @@ def matmul_lhsT_rhs(lhs_T: np.ndarray, rhs: np.ndarray) -> np.ndarray:
     return lhs_T.astype(np.float32).T @ rhs.astype(np.float32)
 
 
+def matmul_lhs_rhs(lhs: np.ndarray, rhs: np.ndarray) -> np.ndarray:
+    """``lhs @ rhs`` as the reference computes it: DMATranspose of lhs, then the same Matmul
+    (kernel_library/matmul/lhs_rhs/kernel_handtuned_89.26mfu.py:226-287; ops/dma_transpose.py:40-42)."""
+    lhs_t = np.array(lhs).T
+    return lhs_t.astype(np.float32).T @ rhs.astype(np.float32)
+
+
 def rmsnorm_matmul(x: np.ndarray, gamma: np.ndarray | None, weight: np.ndarray, eps: float) -> np.ndarray:
     """``(x * rsqrt(mean_k x^2 + eps) * gamma) @ weight`` as the reference's op chain:
 

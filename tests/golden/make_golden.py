@@ -146,6 +146,13 @@ def main() -> None:
     print("hand rmsnorm kernel vs SSA op simulator (gamma absent), max abs diff:", float(np.abs(full - ssa).max()))
     out["ssa_rmsnorm_2048_seed0_sample"] = ssa[::127, ::131].copy()
 
+    # 7. the lhs . rhs hand kernel (K-major lhs, DMA-transposed upstream) at 2048^3, seed 0
+    t = draw(0, [("lhs", (2048, 2048), {"kind": "normal"}), ("rhs", (2048, 2048), {"kind": "normal"})])
+    lr = _load_file(ref / "kernel_library/matmul/lhs_rhs/kernel_handtuned_89.26mfu.py", "ref_matmul_lhs_rhs")
+    full = np.asarray(simulate_fp32(lr.matmul_lhs_rhs_nkigym)(t["lhs"], t["rhs"]), dtype=np.float32)
+    out["hand_matmul_lhs_rhs_2048_seed0_sample"] = full[::127, ::131].copy()
+    print("hand lhs.rhs kernel vs numpy, max abs diff:", float(np.abs(full - t["lhs"] @ t["rhs"]).max()))
+
     np.savez_compressed(HERE / "reference_outputs.npz", **out)
     for k, v in out.items():
         print(f"{k:45s} {v.shape} {v.dtype}")

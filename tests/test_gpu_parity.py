@@ -143,6 +143,23 @@ def test_linearity_and_determinism_full_size(K):
     assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
 
 
+# ---- matmul_lhs_rhs (K-major lhs) --------------------------------------------------------------
+@pytest.mark.parametrize("k,m,n", [(64, 128, 64), (512, 256, 384), (520, 1000, 1016), (2048, 2048, 2048), (72, 136, 200)])
+@pytest.mark.parametrize("c", [cfg(128, 128, 64, 4), cfg(128, 256, 128, 2), cfg(256, 256, 64, 4, cm=2), cfg(256, 128, 64, 3), None],
+                         ids=["1cta", "1cta-k128", "pair", "msub2", "default"])
+def test_matmul_lhs_rhs(K, k, m, n, c):
+    t = O.generate_inputs(7, [("lhs", (m, k), N_(k)), ("rhs", (k, n), N_(k))], bf16=True)
+    got = K.to_host(K.matmul_lhs_rhs(K.to_device(t["lhs"].astype(BF)), K.to_device(t["rhs"].astype(BF)), cfg=c)).astype(np.float32)
+    assert O.max_abs_rel_err(got, O.matmul_lhs_rhs(t["lhs"], t["rhs"])) <= TOL_BF16
+
+
+def test_matmul_lhs_rhs_hand_kernel_shape_2048(K, golden):
+    t = O.generate_inputs(0, [("lhs", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
+    got = K.to_host(K.matmul_lhs_rhs(K.to_device(t["lhs"].astype(BF)), K.to_device(t["rhs"].astype(BF)))).astype(np.float32)
+    sample, ref = got[::127, ::131], golden["hand_matmul_lhs_rhs_2048_seed0_sample"]
+    assert np.max(np.abs(sample - ref)) / np.sqrt(np.mean(ref * ref)) <= 3e-2   # bf16 input rounding vs fp32 golden
+
+
 # ---- fused RMSNorm + matmul ------------------------------------------------------------------
 def _rms_case(K, seed, m, k, n, eps, c, gamma=True):
     t = O.generate_inputs(seed, [("x", (m, k), None), ("gamma", (k,), U), ("weight", (k, n), N_(k))], bf16=True)

@@ -60,6 +60,17 @@ def test_profile_fp32_config_and_rmsnorm(native_lib):
     assert len(out.successes) == 1, [f.hardware_output[-300:] for f in out.failures]
 
 
+def test_profile_matmul_lhs_rhs_family(native_lib):
+    from autotune.runner.api import profile
+    from autotune.runner.candidate import Candidate, jobs_from_candidates
+
+    d = {"kind": "normal", "scale": 512 ** -0.5}
+    cands = [Candidate("matmul_lhs_rhs", dict(tile_m=tm, tile_n=256, tile_k=64, stages=3, cluster_m=cm)) for tm, cm in ((128, 1), (256, 2))]
+    out = profile(jobs_from_candidates(cands, (768, 512), {"lhs": ((768, 512), "bfloat16", d), "rhs": ((512, 512), "bfloat16", d)}),
+                  "", 5, "b200", False, warmup=1, iters=3)
+    assert len(out.successes) == 2, [f.hardware_output[-300:] for f in out.failures]
+
+
 def test_vendor_baseline_row(native_lib, tmp_path):
     from autotune.runner.baseline import profile_numpy_baseline
 

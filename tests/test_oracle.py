@@ -67,6 +67,13 @@ def test_hand_kernels_2048_samples(golden):
                                atol=5e-2, rtol=1e-4)
 
 
+def test_matmul_lhs_rhs_hand_kernel_sample(golden):
+    t = O.generate_inputs(0, [("lhs", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=False)
+    got = O.matmul_lhs_rhs(t["lhs"], t["rhs"])
+    np.testing.assert_allclose(got[::127, ::131], golden["hand_matmul_lhs_rhs_2048_seed0_sample"], atol=5e-3, rtol=5e-3)
+    assert np.array_equal(got, t["lhs"] @ t["rhs"])
+
+
 def test_error_metric_edge_cases():
     e = np.zeros((4, 4), dtype=np.float32)
     assert O.max_abs_rel_err(e, e) == 0.0
