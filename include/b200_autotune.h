@@ -43,9 +43,9 @@ typedef enum b200_status {
  * KernelJob.lnc (autotune/src/autotune/runner/types.py:50). */
 typedef struct b200_cfg {
   int tile_m;     /* output-tile rows per CTA group: 128 or 256                            */
-  int tile_n;     /* output-tile columns: 32..256, multiple of 32 (16 for the skinny path) */
-  int tile_k;     /* K extent of one pipeline stage: 64 or 128                             */
-  int stages;     /* depth of the TMA -> shared-memory ring, 2..12                          */
+  int tile_n;     /* output-tile columns: 64..256, a multiple of 64 per CTA (128 per pair)  */
+  int tile_k;     /* K extent of one pipeline stage: 64 or 128 (plain GEMM also 32, 96)     */
+  int stages;     /* depth of the TMA -> shared-memory ring, 1..12                          */
   int cluster_m;  /* 1, or 2 = a CTA pair along M (tile_m 256: one 2-SM UMMA)               */
   int cluster_n;  /* 1 (reserved)                                                          */
   int swizzle;    /* tile rasterisation group width along M (1,2,4,8,16); 0 = default      */
@@ -111,7 +111,8 @@ int b200_matmul_lhsT_rhs_f32(const void* lhsT, const void* rhs, void* out,
 
 /* out[M,N] (bf16) = (x / sqrt(mean_k x^2 + eps) * gamma) . w with x[M,K] (K contiguous),
  * gamma[K] (bf16, may be NULL = all ones), w[K,N] (N contiguous); row statistics and
- * accumulation in fp32.
+ * accumulation in fp32.  M <= 16 runs the weight-streaming kernel (only tile_k and stages of
+ * cfg apply) and needs b200_workspace_bytes of zero-filled scratch; M > 16 see b200_cfg.norm_mode.
  * Replaces rmsnorm_matmul_online, kernel_library/rmsnorm_matmul/kernel_hand_online.py:198-353
  * (gamma is an extension; gamma == NULL reproduces that kernel's maths). */
 int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out,

@@ -282,22 +282,38 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
           // last contribution to this tile: every partial is visible; scale, store, and leave
           // scratch and counter zero for the next launch
           __threadfence();
-          // all 16 loads of a column are issued before the first store: the loop is otherwise
-          // one L2 round trip per cell (loads cannot be hoisted over possibly-aliasing stores)
-          for (int c = 0; c < SKINNY_TILE_N / 32; ++c) {
-            const int nn = n0 + c * 32 + lane;
-            if (nn < p.N) {
-              float sums[SKINNY_ROWS];
+          // 16-byte loads, 16 of them (8 rows x 256 columns) in flight per lane before the first
+          // store: one L2 round trip per cell would otherwise dominate the kernel's tail (the
+          // compiler cannot hoist loads over possibly-aliasing stores).  N is a multiple of 8, so a
+          // group of four columns never straddles N.
+          static_assert(SKINNY_TILE_N == 256 && SKINNY_ROWS == 16, "finalize covers 2 x 128 columns, 2 x 8 rows");
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            float4 v[8][2];
 #pragma unroll
-              for (int m = 0; m < SKINNY_ROWS; ++m)
-                sums[m] = (m < p.M) ? __ldcg(p.scratch + static_cast<long long>(m) * p.N + nn) : 0.0f;
+            for (int r = 0; r < 8; ++r)
 #pragma unroll
-              for (int m = 0; m < SKINNY_ROWS; ++m)
-                if (m < p.M) {
-                  p.out[static_cast<long long>(m) * p.N + nn] = __float2bfloat16(sums[m] * ctrl->rinv[m]);
-                  __stcg(p.scratch + static_cast<long long>(m) * p.N + nn, 0.0f);
+              for (int j = 0; j < 2; ++j) {
+                const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
+                v[r][j] = (m < p.M && nn < p.N)
+                              ? __ldcg(reinterpret_cast<const float4*>(p.scratch + static_cast<long long>(m) * p.N + nn))
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
+                if (m < p.M && nn < p.N) {
+                  const float ri = ctrl->rinv[m];
+                  uint2 o;
+                  o.x = pack_bf16x2(v[r][j].x * ri, v[r][j].y * ri);
+                  o.y = pack_bf16x2(v[r][j].z * ri, v[r][j].w * ri);
+                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + nn) = o;
+                  __stcg(reinterpret_cast<float4*>(p.scratch + static_cast<long long>(m) * p.N + nn),
+                         make_float4(0.f, 0.f, 0.f, 0.f));
                 }
-            }
+              }
           }
           if (lane == 0) p.tile_count[nt] = 0;
         }
