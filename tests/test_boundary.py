@@ -95,7 +95,8 @@ def test_candidate_round_trip_and_grid():
     c = Candidate("rmsnorm_matmul", {"tile_m": 128, "tile_n": 256, "tile_k": 64, "stages": 4}, {"eps": 1e-6})
     back = parse_source(c.to_source())
     assert back.family == c.family and back.config["tile_n"] == 256 and back.scalars == {"eps": 1e-6}
-    assert back.config["cluster_m"] == 1
+    assert back.config["cluster_m"] == 1 and back.config["norm_mode"] == 0
+    assert parse_source(Candidate("matmul_lhs_rhs", {"tile_m": 128, "norm_mode": 2}).to_source()).config["norm_mode"] == 2
     grid = enumerate_grid("matmul_lhsT_rhs")
     assert len(grid) == 64 and len({tuple(sorted(g.config.items())) for g in grid}) == 64
     with pytest.raises(ValueError):
@@ -130,6 +131,33 @@ def test_cfg_check_budgets(native_lib):
     accepted = sum(native.cfg_check("matmul_lhsT_rhs", c.config, 8192, 8192, 8192)[0] == native.OK
                    for c in enumerate_grid("matmul_lhsT_rhs"))
     assert 0 < accepted < 64  # the grid holds both runnable and over-subscribed points
+
+
+def test_cfg_check_families_and_scratch_sizes(native_lib):
+    import ctypes as C
+
+    from autotune import native
+
+    lib = native.load()
+    pair = dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2)
+    assert native.cfg_check("matmul_lhs_rhs", pair, 4096, 4096, 4096)[0] == native.OK
+    assert native.cfg_check("matmul_lhs_rhs", dict(pair, tile_k=32), 4096, 4096, 4096)[0] == native.ERR_UNSUPPORTED
+    assert native.cfg_check("matmul_lhs_rhs", pair, 4096, 4096, 4100)[0] == native.ERR_BAD_SHAPE
+    # fused kernel: the skinny path only looks at tile_k / stages; larger M follows norm_mode
+    assert native.cfg_check("rmsnorm_matmul", dict(tile_m=16, tile_n=256, tile_k=128, stages=3), 16, 28672, 8192)[0] == native.OK
+    assert native.cfg_check("rmsnorm_matmul", dict(tile_m=16, tile_n=256, tile_k=128, stages=4), 16, 28672, 8192)[0] == native.ERR_SMEM_OOM
+    assert native.cfg_check("rmsnorm_matmul", dict(pair, norm_mode=2), 4096, 11008, 4096)[0] == native.OK
+    assert native.cfg_check("rmsnorm_matmul", dict(pair, norm_mode=1, stages=6), 4096, 11008, 4096)[0] == native.ERR_SMEM_OOM
+    assert native.cfg_check("rmsnorm_matmul", dict(pair, norm_mode=2), 4096, 11008, 4100)[0] == native.ERR_BAD_SHAPE
+
+    def ws(cfg, M, N, K):
+        c = native.Cfg.from_dict(cfg)
+        return lib.b200_workspace_bytes(b"rmsnorm_matmul", C.byref(c) if c is not None else None, M, N, K)
+
+    assert ws(None, 16, 28672, 8192) >= 16 * 28672 * 4 + 112 * 4
+    assert ws(dict(pair, norm_mode=1), 4096, 11008, 4096) == 0
+    assert ws(dict(pair, norm_mode=2), 4096, 11008, 4096) >= 4096 * 4096 * 2 + 4096 * 4
+    assert lib.b200_workspace_bytes(b"matmul_lhsT_rhs", None, 8192, 8192, 8192) == 0
 
 
 def test_compile_one_reports_rejections(native_lib, tmp_path):
