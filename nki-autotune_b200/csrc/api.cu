@@ -134,9 +134,10 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
   p.tile_k = cfg.tile_k;
   p.stages = cfg.stages;
   const int nc = cfg.tile_n / p.cta_group;
-  if (cfg.tile_n < 64 || cfg.tile_n > 256 || cfg.tile_n % 32 != 0 || nc % 64 != 0)
+  const bool wide = (cfg.tile_n == 512 && fam == FAM_LHST);  // two 256-column UMMAs side by side
+  if (!wide && (cfg.tile_n < 64 || cfg.tile_n > 256 || cfg.tile_n % 32 != 0 || nc % 64 != 0))
     return set_error(B200_ERR_UNSUPPORTED,
-                     "tile_n=%d: need a multiple of %d in [64,256] (64-column operand chunks per CTA)",
+                     "tile_n=%d: need a multiple of %d in [64,256] (64-column operand chunks per CTA), or 512",
                      cfg.tile_n, 64 * p.cta_group);
   if ((fam == FAM_RMSNORM || prologue || lhs_kmajor) ? (cfg.tile_k != 64 && cfg.tile_k != 128)
                          : (cfg.tile_k != 32 && cfg.tile_k != 64 && cfg.tile_k != 96 && cfg.tile_k != 128))
@@ -442,6 +443,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   gp.N = static_cast<int>(la.N);
   gp.K = static_cast<int>(la.K);
   gp.tile_n = plan.tile_n;
+  gp.umma_n = plan.tile_n > 256 ? plan.tile_n / 2 : plan.tile_n;
   gp.tile_k = plan.tile_k;
   gp.stages = plan.stages;
   gp.num_m_tiles = static_cast<int>((la.M + plan.tile_m - 1) / plan.tile_m);

@@ -34,6 +34,7 @@ constexpr int DEBUG_NO_MMA = 3;         // loads and barriers run, the UMMAs are
 struct GemmParams {
   int M, N, K;
   int tile_n, tile_k, stages;
+  int umma_n;        // N of one UMMA: tile_n, or tile_n / 2 when the tile is two instructions wide (tile_n 512)
   int num_m_tiles;   // tiles of (128 * M_SUB * CTA_GROUP) rows
   int num_n_tiles;
   int num_k_blocks;
@@ -153,6 +154,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int tile_k = p.tile_k;
   const int stages = p.stages;
   const int nc = tile_n / CTA_GROUP;  // columns of the B tile this CTA loads
+  const int umma_n = p.umma_n;
+  const int n_sub = tile_n / umma_n;           // UMMAs side by side along N (1 or 2)
+  const int nc_sub = umma_n / CTA_GROUP;       // columns this CTA supplies to one of them
   const uint32_t a_bytes = static_cast<uint32_t>(MC) * tile_k * 2u;
   const uint32_t b_bytes = static_cast<uint32_t>(nc) * tile_k * 2u;
 
@@ -285,7 +289,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         int mt, nt;
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
-        const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc;
+        const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc_sub;  // first UMMA's share; next at + umma_n
         for (int kb = 0; kb < num_k_blocks; ++kb, ++it, ring.advance(stages)) {
           const uint32_t s = ring.s;
           const uint32_t ph = ring.ph;
@@ -308,8 +312,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               for (int c = 0; c < MC / 64; ++c)
                 tma_load_2d_pair(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
             }
-            for (int c = 0; c < nc / 64; ++c)
-              tma_load_2d_pair(b_s + c * tile_k * 128, &tm_b, full_leader, n_base + 64 * c, k0);
+            for (int ns = 0; ns < n_sub; ++ns)
+              for (int c = 0; c < nc_sub / 64; ++c)
+                tma_load_2d_pair(b_s + (ns * (nc_sub / 64) + c) * tile_k * 128, &tm_b, full_leader,
+                                 n_base + ns * umma_n + 64 * c, k0);
           } else {
             mbar_arrive_expect_tx(full_local, a_bytes + b_bytes);
             if constexpr (A_KMAJOR) {
@@ -319,8 +325,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               for (int c = 0; c < MC / 64; ++c)
                 tma_load_2d(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
             }
-            for (int c = 0; c < nc / 64; ++c)
-              tma_load_2d(b_s + c * tile_k * 128, &tm_b, full_local, n_base + 64 * c, k0);
+            for (int ns = 0; ns < n_sub; ++ns)
+              for (int c = 0; c < nc_sub / 64; ++c)
+                tma_load_2d(b_s + (ns * (nc_sub / 64) + c) * tile_k * 128, &tm_b, full_local,
+                            n_base + ns * umma_n + 64 * c, k0);
           }
         }
       }
@@ -336,13 +344,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     if (lane == 0 && cta_rank == 0) {
       wctx.role = ROLE_MMA;
       const uint32_t idesc =
-          make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, A_KMAJOR ? 0 : 1, 1);
+          make_idesc_bf16_f32(128 * CTA_GROUP, umma_n, A_KMAJOR ? 0 : 1, 1);
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
       // descriptors: the high word (stride offset, version, swizzle) and the leading offset are
       // fixed; only the 14-bit start-address field moves (16-byte units: 128 per 16 k-rows)
       const uint64_t a_desc0 = make_smem_desc_sw128(a_base, mn_lbo, 1024);
       const uint64_t b_desc0 = make_smem_desc_sw128(b_base, mn_lbo, 1024);
       const uint32_t a_step = a_bytes >> 4, b_step = b_bytes >> 4, sub_step = (2u * mn_lbo) >> 4;
+      const uint32_t nsub_step = (static_cast<uint32_t>(nc_sub / 64) * mn_lbo) >> 4;  // next UMMA's B chunks
       const int nk16 = tile_k / 16;
       const bool issue = p.debug_mode != DEBUG_NO_MMA;
       Ring ring, acc;
@@ -369,8 +378,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 if constexpr (A_KMAJOR)  // K-major x tile: 64-wide k chunks of MC rows x 128 B, 32 B per 16 k
                   ad = make_smem_desc_sw128(a_base + s * a_bytes + (k16 >> 2) * (MC * 128) + mi * (128 * 128) +
                                                 (k16 & 3) * 32, 16, 1024);
-                umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n), ad, bdesc, idesc,
-                                     (kb | k16) != 0 ? 1u : 0u);
+                for (int ns = 0; ns < n_sub; ++ns)
+                  umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n + ns * umma_n), ad,
+                                       bdesc + ns * nsub_step, idesc, (kb | k16) != 0 ? 1u : 0u);
               }
             }
           }

@@ -96,6 +96,12 @@ def test_bf16_edges_and_sizes(K, k, m, n, c):
     assert _mm_case(K, 6, k, m, n, c) <= TOL_BF16
 
 
+@pytest.mark.parametrize("k,m,n", [(64, 256, 512), (520, 1000, 1016), (1024, 512, 2048)])
+@pytest.mark.parametrize("c", [cfg(256, 512, 64, 4, cm=2), cfg(128, 512, 64, 2), cfg(256, 512, 128, 2, cm=2)], ids=["pair", "1cta", "pair-k128"])
+def test_bf16_wide_tiles_two_ummas_along_n(K, k, m, n, c):
+    assert _mm_case(K, 9, k, m, n, c) <= TOL_BF16
+
+
 def test_bf16_hand_kernel_shape_2048(K, golden):
     """2048^3, the only shape the reference's hand kernel accepts, against its simulated output."""
     t = O.generate_inputs(0, [("lhs_T", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
