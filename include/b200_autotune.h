@@ -81,7 +81,9 @@ int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long
                    long* smem_bytes, int* tmem_cols);
 
 /* Bytes of device scratch the candidate can use (0 when it needs none).  The scratch must be
- * zero-filled once before first use; the kernels leave it reusable for the next launch. */
+ * zero-filled once before first use; the kernels leave it reusable for the next launch.  After
+ * a launch that ended with B200_ERR_DEVICE_WAIT its contents are undefined: zero it again.
+ * Launches that share one scratch buffer must not overlap on the GPU. */
 size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K);
 
 /* C[M,N] (bf16, row stride ld_out) = lhsT[K,M]^T . rhs[K,N], bf16 operands, fp32
