@@ -42,10 +42,10 @@ WORKLOAD = "configs[1]: matmul_lhsT_rhs bf16 lhsT[8192,8192] rhs[8192,8192], N(0
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.186e9  # profiles/gemm_tcgen05_matmul_lhsT_rhs_8192.md
 
 SHORTLIST = [
+    dict(tile_m=512, tile_n=256, tile_k=64, stages=4, cluster_m=2),
+    dict(tile_m=256, tile_n=512, tile_k=64, stages=4, cluster_m=2),
     dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2),
-    dict(tile_m=256, tile_n=256, tile_k=64, stages=6, cluster_m=2),
     dict(tile_m=128, tile_n=256, tile_k=128, stages=2, cluster_m=1),
-    dict(tile_m=128, tile_n=256, tile_k=64, stages=4, cluster_m=1),
 ]
 
 

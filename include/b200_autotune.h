@@ -42,12 +42,13 @@ typedef enum b200_status {
  * counts, SoftwarePipeline stages, Reorder; nkigym/src/nkigym/transforms/*.py) and of
  * KernelJob.lnc (autotune/src/autotune/runner/types.py:50). */
 typedef struct b200_cfg {
-  int tile_m;     /* output-tile rows per CTA group: 128 or 256                            */
+  int tile_m;     /* output-tile rows per CTA group: 128 or 256; 512 with cluster_m 2 (plain GEMM
+                     families: two 2-SM UMMAs along M share each B tile, single accumulator buffer) */
   int tile_n;     /* output-tile columns: 64..256, a multiple of 64 per CTA (128 per pair);
                      512 = two 256-column UMMAs side by side (single accumulator buffer)     */
   int tile_k;     /* K extent of one pipeline stage: 64 or 128 (plain GEMM also 32, 96)     */
   int stages;     /* depth of the TMA -> shared-memory ring, 1..12                          */
-  int cluster_m;  /* 1, or 2 = a CTA pair along M (tile_m 256: one 2-SM UMMA)               */
+  int cluster_m;  /* 1, or 2 = a CTA pair along M (tile_m 256 or 512: 2-SM UMMAs)           */
   int cluster_n;  /* 1 (reserved)                                                          */
   int swizzle;    /* tile rasterisation group width along M (1,2,4,8,16); 0 = default      */
   int split_k;    /* reserved (the skinny kernel balances K ranges itself); 0               */

@@ -6,6 +6,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -70,6 +71,8 @@ static b200_cfg default_cfg(Family fam, long M) {
     c.tile_m = 16; c.tile_n = 256; c.tile_k = 128; c.stages = 3; c.cluster_m = 1;
   } else if (fam == FAM_RMSNORM) {
     c.tile_m = 128; c.tile_n = 256; c.tile_k = 128; c.stages = 2; c.cluster_m = 1;
+  } else if (M >= 2048) {  // enough rows for 512-row pair tiles: least operand traffic per flop
+    c.tile_m = 512; c.tile_n = 256; c.tile_k = 64; c.stages = 4; c.cluster_m = 2;
   } else {
     c.tile_m = 256; c.tile_n = 256; c.tile_k = 128; c.stages = 3; c.cluster_m = 2;
   }
@@ -115,8 +118,9 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
   if (prologue || lhs_kmajor) fam = FAM_LHST;  // same pipeline budgets as the plain GEMM
   const int cluster_m = cfg.cluster_m == 0 ? 1 : cfg.cluster_m;
   const int cluster_n = cfg.cluster_n == 0 ? 1 : cfg.cluster_n;
-  if (cfg.tile_m != 128 && cfg.tile_m != 256)
-    return set_error(B200_ERR_UNSUPPORTED, "tile_m=%d: only 128 and 256 are implemented", cfg.tile_m);
+  if (cfg.tile_m != 128 && cfg.tile_m != 256 && !(cfg.tile_m == 512 && cluster_m == 2 && fam == FAM_LHST))
+    return set_error(B200_ERR_UNSUPPORTED,
+                     "tile_m=%d: only 128, 256 and (plain GEMM, CTA pair) 512 are implemented", cfg.tile_m);
   if (cluster_m != 1 && cluster_m != 2)
     return set_error(B200_ERR_UNSUPPORTED, "cluster_m=%d: only 1 and 2 are implemented", cluster_m);
   if (cluster_n != 1)
@@ -127,7 +131,8 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
   p.a_kmajor = lhs_kmajor ? 1 : 0;
   p.cluster = cluster_m;
   p.tile_m = cfg.tile_m;
-  if (cluster_m == 2 && cfg.tile_m == 256) { p.cta_group = 2; p.m_sub = 1; }
+  if (cluster_m == 2 && cfg.tile_m == 512) { p.cta_group = 2; p.m_sub = 2; }  // two pair-UMMAs per k-step
+  else if (cluster_m == 2 && cfg.tile_m == 256) { p.cta_group = 2; p.m_sub = 1; }
   else if (cfg.tile_m == 256) { p.cta_group = 1; p.m_sub = 2; }
   else { p.cta_group = 1; p.m_sub = 1; }
   p.tile_n = cfg.tile_n;
@@ -146,7 +151,7 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     return set_error(B200_ERR_UNSUPPORTED, "stages=%d: need 1..%d", cfg.stages, MAX_STAGES);
   if (cfg.swizzle < 0 || cfg.swizzle > 64)
     return set_error(B200_ERR_UNSUPPORTED, "swizzle=%d: need 0..64", cfg.swizzle);
-  p.group_m = cfg.swizzle > 0 ? cfg.swizzle : (p.cta_group == 2 || p.m_sub == 2 ? 8 : 16);
+  p.group_m = cfg.swizzle > 0 ? cfg.swizzle : (cfg.tile_m == 512 ? 4 : (p.cta_group == 2 || p.m_sub == 2 ? 8 : 16));
 
   const int acc_cols = p.m_sub * p.tile_n;
   const long mc = 128L * p.m_sub;
@@ -251,15 +256,18 @@ typedef void (*RmsKernelFn)(const CUtensorMap, const CUtensorMap, const RmsParam
 
 static GemmKernelFn pick_gemm_kernel(const Plan& p) {
   if (p.prologue) {
+    if (p.cta_group == 2 && p.m_sub == 2) return gemm_tcgen05_kernel<2, 2, A_NORM>;
     if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, A_NORM>;
     if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, A_NORM>;
     return gemm_tcgen05_kernel<1, 1, A_NORM>;
   }
   if (p.a_kmajor) {
+    if (p.cta_group == 2 && p.m_sub == 2) return gemm_tcgen05_kernel<2, 2, A_KMAJOR_PLAIN>;
     if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1, A_KMAJOR_PLAIN>;
     if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2, A_KMAJOR_PLAIN>;
     return gemm_tcgen05_kernel<1, 1, A_KMAJOR_PLAIN>;
   }
+  if (p.cta_group == 2 && p.m_sub == 2) return gemm_tcgen05_kernel<2, 2>;
   if (p.cta_group == 2) return gemm_tcgen05_kernel<2, 1>;
   if (p.m_sub == 2) return gemm_tcgen05_kernel<1, 2>;
   return gemm_tcgen05_kernel<1, 1>;
@@ -459,6 +467,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (cfg && cfg->reserved[1] > 0) limit_us = cfg->reserved[1];
   gp.timeout_cycles = limit_us * (di.clock_khz > 0 ? di.clock_khz / 1000 : 1900);
   gp.debug_mode = cfg ? cfg->reserved[0] : 0;
+  gp.record_clocks = cfg ? cfg->reserved[2] : 0;
   if (plan.prologue) {
     gp.x = static_cast<const __nv_bfloat16*>(la.a);
     gp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
@@ -533,6 +542,9 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (groups > units) groups = units;
   if (groups < 1) groups = 1;
   pr->grid = dim3(static_cast<unsigned>(groups * plan.cluster));
+  if (getenv("B200_AUTOTUNE_DEBUG") != nullptr)
+    fprintf(stderr, "[b200] %d SMs, cluster %d, CTA groups %ld (work units %ld), grid %u, block %u, smem %zu\n",
+            di.sm_count, plan.cluster, groups, units, pr->grid.x, pr->block.x, pr->smem);
   return B200_OK;
 }
 

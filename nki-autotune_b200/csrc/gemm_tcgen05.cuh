@@ -18,6 +18,7 @@
 // Every wait is bounded: when a wait gives up it records where in status[] and raises a
 // CTA-wide abort flag so every role leaves its loop and the CTA frees its tensor memory.
 #pragma once
+#include <type_traits>
 #include <cuda.h>
 #include "ptx_sm100.cuh"
 
@@ -46,6 +47,7 @@ struct GemmParams {
   int* status;       // B200_DEV_STATUS_INTS ints or nullptr
   long long timeout_cycles;
   int debug_mode;    // 0, or one of the DEBUG_* hooks
+  int record_clocks; // measurement aid: status[6]/[7] = longest CTA lifetime in SM cycles / nanoseconds
   // NORM variant only (fused RMSNorm with an in-kernel prologue):
   const __nv_bfloat16* x;      // [M,K] activations
   const __nv_bfloat16* gamma;  // [K] or nullptr
@@ -173,6 +175,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int first_tile = static_cast<int>(blockIdx.x) / CTA_GROUP;
   const int tile_stride = static_cast<int>(gridDim.x) / CTA_GROUP;
 
+  long long life_c0 = 0;
+  unsigned long long life_n0 = 0;
+  if (p.record_clocks && threadIdx.x == 0) {
+    life_c0 = clock64();
+    life_n0 = global_timer_ns();
+  }
   // ------------------------------------------------------------------ set-up
   if (threadIdx.x == 0) {
     ctrl->abort_flag = 0;
@@ -285,6 +293,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t it = 0;
       Ring ring;
       bool ok = true;
+      const int b_chunks = nc / 64, sub_chunks = nc_sub / 64, sub_jump = umma_n - nc_sub;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
         int mt, nt;
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
@@ -312,10 +321,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               for (int c = 0; c < MC / 64; ++c)
                 tma_load_2d_pair(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
             }
-            for (int ns = 0; ns < n_sub; ++ns)
-              for (int c = 0; c < nc_sub / 64; ++c)
-                tma_load_2d_pair(b_s + (ns * (nc_sub / 64) + c) * tile_k * 128, &tm_b, full_leader,
-                                 n_base + ns * umma_n + 64 * c, k0);
+            // B chunks of 64 columns; after this CTA's share of one UMMA the column jumps to the next UMMA
+            for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
+              tma_load_2d_pair(b_s + c * tile_k * 128, &tm_b, full_leader, col, k0);
+              col += 64;
+              if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
+            }
           } else {
             mbar_arrive_expect_tx(full_local, a_bytes + b_bytes);
             if constexpr (A_KMAJOR) {
@@ -325,10 +336,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               for (int c = 0; c < MC / 64; ++c)
                 tma_load_2d(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
             }
-            for (int ns = 0; ns < n_sub; ++ns)
-              for (int c = 0; c < nc_sub / 64; ++c)
-                tma_load_2d(b_s + (ns * (nc_sub / 64) + c) * tile_k * 128, &tm_b, full_local,
-                            n_base + ns * umma_n + 64 * c, k0);
+            for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
+              tma_load_2d(b_s + c * tile_k * 128, &tm_b, full_local, col, k0);
+              col += 64;
+              if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
+            }
           }
         }
       }
@@ -369,7 +381,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           tc_fence_after();
           uint64_t adesc = a_desc0 + s * a_step;
           uint64_t bdesc = b_desc0 + s * b_step;
-          if (issue) {
+          // one k-block of UMMAs; NS (instructions side by side along N) is a compile-time constant so
+          // that the common NS = 1 loop unrolls into a straight run of instructions
+          auto issue_k_block = [&](auto ns_const) {
+            constexpr int NS = decltype(ns_const)::value;
 #pragma unroll 4
             for (int k16 = 0; k16 < nk16; ++k16, adesc += 128, bdesc += 128) {
 #pragma unroll
@@ -378,11 +393,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                 if constexpr (A_KMAJOR)  // K-major x tile: 64-wide k chunks of MC rows x 128 B, 32 B per 16 k
                   ad = make_smem_desc_sw128(a_base + s * a_bytes + (k16 >> 2) * (MC * 128) + mi * (128 * 128) +
                                                 (k16 & 3) * 32, 16, 1024);
-                for (int ns = 0; ns < n_sub; ++ns)
+#pragma unroll
+                for (int ns = 0; ns < NS; ++ns)
                   umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n + ns * umma_n), ad,
                                        bdesc + ns * nsub_step, idesc, (kb | k16) != 0 ? 1u : 0u);
               }
             }
+          };
+          if (issue) {
+            if (n_sub == 1) issue_k_block(std::integral_constant<int, 1>{});
+            else issue_k_block(std::integral_constant<int, 2>{});
           }
           if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->empty[s]), 3);
           else umma_commit_1cta(smem_u32(&ctrl->empty[s]));
@@ -467,6 +487,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<CTA_GROUP>(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+  if (p.record_clocks && threadIdx.x == 0 && p.status != nullptr) {
+    atomicMax(&p.status[6], static_cast<int>(clock64() - life_c0));
+    atomicMax(&p.status[7], static_cast<int>(global_timer_ns() - life_n0));
   }
 }
 

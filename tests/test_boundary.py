@@ -125,6 +125,12 @@ def test_cfg_check_budgets(native_lib):
     oom = native.cfg_check("matmul_lhsT_rhs", dict(tile_m=128, tile_n=256, tile_k=64, stages=5, cluster_m=1), 8192, 8192, 8192)
     assert oom[0] == native.ERR_SMEM_OOM and "Out of memory in smem" in oom[1] and oom[2] > 232448
     assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=96, tile_n=256, tile_k=64, stages=4))[0] == native.ERR_UNSUPPORTED
+    # 512-row tiles exist only as a CTA pair issuing two UMMAs along M; all 512 accumulator columns are in use
+    tall = native.cfg_check("matmul_lhsT_rhs", dict(tile_m=512, tile_n=256, tile_k=64, stages=4, cluster_m=2))
+    assert tall[0] == native.OK and tall[3] == 512
+    assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=512, tile_n=256, tile_k=64, stages=4, cluster_m=1))[0] == native.ERR_UNSUPPORTED
+    assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=512, tile_n=256, tile_k=64, stages=5, cluster_m=2))[0] == native.ERR_SMEM_OOM
+    assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=512, tile_n=512, tile_k=64, stages=2, cluster_m=2))[0] == native.ERR_TMEM_OOM
     assert native.cfg_check("matmul_lhsT_rhs", dict(tile_m=128, tile_n=256, tile_k=64, stages=4), 100, 64, 64)[0] == native.ERR_BAD_SHAPE
     assert native.cfg_check("nope", None)[0] == native.ERR_BAD_ARG
     assert native.cfg_check("rmsnorm_matmul", None, 4096, 11008, 4096)[0] == native.OK

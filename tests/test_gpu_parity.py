@@ -102,6 +102,13 @@ def test_bf16_wide_tiles_two_ummas_along_n(K, k, m, n, c):
     assert _mm_case(K, 9, k, m, n, c) <= TOL_BF16
 
 
+@pytest.mark.parametrize("k,m,n", [(64, 512, 256), (520, 1000, 1016), (1024, 2048, 512), (2048, 2048, 2048)])
+@pytest.mark.parametrize("c", [cfg(512, 256, 64, 4, cm=2), cfg(512, 256, 128, 2, cm=2), cfg(512, 128, 64, 4, cm=2)],
+                         ids=["512x256", "512x256-k128", "512x128"])
+def test_bf16_tall_pair_tiles_two_ummas_along_m(K, k, m, n, c):
+    assert _mm_case(K, 10, k, m, n, c) <= TOL_BF16
+
+
 def test_bf16_hand_kernel_shape_2048(K, golden):
     """2048^3, the only shape the reference's hand kernel accepts, against its simulated output."""
     t = O.generate_inputs(0, [("lhs_T", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
