@@ -165,6 +165,14 @@ class Ranks:
         self.dist.gather_object(obj, out, dst=0)
         return out
 
+    def nccl_group(self):
+        """NCCL group over the same ranks, for the device-side replication / gather of the row split."""
+        if self.dist is None:
+            return None
+        if getattr(self, "_nccl", None) is None:
+            self._nccl = self.dist.new_group(backend="nccl")
+        return self._nccl
+
     def close(self) -> None:
         if self.dist is not None:
             self.dist.destroy_process_group()
@@ -419,7 +427,7 @@ def run_extras(ranks: Ranks, torch, kernels, args) -> dict:
         o = torch.empty(Mx, Nx, dtype=torch.bfloat16, device="cuda")
         xt = x.t().contiguous()
         fused_by_cfg = {}
-        for name, cfg in (("default (prologue, 256x256x128s3c2)", None),
+        for name, cfg in (("default (prologue, 512x256x64s4c2)", None),
                           ("inline 128x256x128s2c1", dict(tile_m=128, tile_n=256, tile_k=128, stages=2, cluster_m=1, norm_mode=1))):
             fused_by_cfg[name] = round(_time_family(kernels, "rmsnorm_matmul", x, w, o, cfg, gamma=gamma, eps=1e-6), 4)
         best_name = min(fused_by_cfg, key=fused_by_cfg.get)
@@ -427,7 +435,7 @@ def run_extras(ranks: Ranks, torch, kernels, args) -> dict:
         kernels.rmsnorm_matmul(x, gamma, w, eps=1e-6, out=o)
         ref = kernels.rmsnorm_matmul_f32(x[:256], gamma, w, 1e-6)
         err = float(((o[:256].float() - ref).abs() / (ref.abs() + ref.pow(2).mean().sqrt())).max())
-        plain = _time_family(kernels, "matmul_lhsT_rhs", xt, w, o, dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2))
+        plain = _time_family(kernels, "matmul_lhsT_rhs", xt, w, o, None)  # library default, same tile as the fused one
         fl = 2.0 * Mx * Nx * Kx
         extras["rmsnorm_matmul_4096x11008x4096"] = {
             "fused_ms": round(fused, 4), "fused_config": best_name, "fused_ms_by_config": fused_by_cfg,
@@ -461,16 +469,45 @@ def run_extras(ranks: Ranks, torch, kernels, args) -> dict:
     m_local = Mt // ranks.world
     a, b = randn(Kx, m_local, scale=Kx ** -0.5), randn(Kx, Nx, scale=Kx ** -0.5)
     o = torch.empty(m_local, Nx, dtype=torch.bfloat16, device="cuda")
-    cfg = dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2)
+    cfg = None  # library default (512x256x64, 4 stages, CTA pair at this M)
     for _ in range(3):
         kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=o)
     ms = timed_region(ranks, torch, lambda: kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=o), 5)
+    row = {
+        "n_gpus": ranks.world, "rows_per_gpu": m_local, "ms": round(ms, 4),
+        "aggregate_tflops": round(2.0 * Mt * Nx * Kx / ms / 1e9, 1), "scaling": "strong",
+    }
+    del o
+    if ranks.world > 1:
+        # the exchange steps around the kernels, over NVLink: rhs uploaded once and broadcast, the row
+        # blocks of C all-gathered into every GPU's memory (kernels read and write local memory only)
+        from autotune import sharded
+
+        grp = ranks.nccl_group()
+        rep = sharded.replicate(b if ranks.rank == 0 else None, (Kx, Nx), torch.bfloat16, "cuda", src=0, group=grp)
+        ms_rep = timed_region(ranks, torch, lambda: sharded.replicate(
+            b if ranks.rank == 0 else None, (Kx, Nx), torch.bfloat16, "cuda", src=0, group=grp), 5)
+        full = torch.empty(Mt, Nx, dtype=torch.bfloat16, device="cuda")
+        step = lambda: sharded.matmul_lhsT_rhs_row_split(a, rep, Mt, cfg=cfg, group=grp, out_full=full)
+        for _ in range(2):
+            step()
+        ms_all = timed_region(ranks, torch, step, 5)
+        # every rank's copy of C must hold every rank's block: compare block checksums through the host
+        sums = [float(full[r * m_local:(r + 1) * m_local].float().sum()) for r in range(ranks.world)]
+        mine = ranks.gather((ranks.rank, sums))
+        if ranks.rank == 0:
+            ref = mine[0][1]
+            row.update({
+                "rhs_broadcast_ms": round(ms_rep, 4), "with_device_allgather_ms": round(ms_all, 4),
+                "aggregate_tflops_with_allgather": round(2.0 * Mt * Nx * Kx / ms_all / 1e9, 1),
+                "allgather_bytes_per_gpu": int(Mt * Nx * 2 * (ranks.world - 1) / ranks.world),
+                "gathered_copies_agree": all(
+                    abs(x - y) <= 1e-6 * max(1.0, abs(y)) for _, s in mine for x, y in zip(s, ref)),
+            })
+        del rep, full
     if ranks.rank == 0:
-        extras["large_m_row_split_131072x4096x4096"] = {
-            "n_gpus": ranks.world, "rows_per_gpu": m_local, "ms": round(ms, 4),
-            "aggregate_tflops": round(2.0 * Mt * Nx * Kx / ms / 1e9, 1), "scaling": "strong",
-        }
-    del a, b, o
+        extras["large_m_row_split_131072x4096x4096"] = row
+    del a, b
 
     # autotune sweep of the 64-point grid at 8192^3, candidates sharded over the ranks
     if args.sweep:

@@ -111,3 +111,70 @@ def test_reference_arm_non_zero_rank_exits_quietly(tmp_path):
     proc = subprocess.run([sys.executable, str(REPO / "bench.py"), "--impl", "reference", "--gpus", "2"],
                           capture_output=True, text=True, timeout=120, env=env)
     assert proc.returncode == 0 and proc.stdout.strip() == ""
+
+
+def test_row_range_covers_m_once_and_keeps_alignment():
+    from autotune.sharded import row_range
+
+    for M, world in [(131072, 8), (1000, 3), (8, 4), (0, 2), (4099, 5)]:
+        bounds = [row_range(M, r, world) for r in range(world)]
+        assert bounds[0][0] == 0 and bounds[-1][1] == M
+        assert all(bounds[i][1] == bounds[i + 1][0] for i in range(world - 1))
+        assert all(b0 % 8 == 0 for b0, _ in bounds)
+    assert row_range(131072, 3, 8) == (49152, 65536)
+    with pytest.raises(ValueError):
+        row_range(10, 2, 2)
+
+
+ROW_SPLIT_SCRIPT = textwrap.dedent(
+    """
+    import sys, json
+    sys.path.insert(0, {pkg!r})
+    import torch, torch.distributed as dist
+    from autotune.sharded import row_range, replicate, matmul_lhsT_rhs_row_split
+
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+
+    def host_matmul(a, b, cfg=None, out=None):   # stand-in for the GPU kernel: the test is about the sharding
+        out.copy_(a.T @ b)
+        return out
+
+    result = {{}}
+    for M in (64, 1000):                          # equal blocks (in-place gather) and ragged blocks
+        K, N = 24, 16
+        g = torch.Generator().manual_seed(5)
+        lhs_T = torch.randn(K, M, generator=g)
+        rhs_src = torch.randn(K, N, generator=g)
+        rhs = replicate(rhs_src if rank == 0 else None, (K, N), torch.float32, "cpu", src=0)
+        m0, m1 = row_range(M, rank, world)
+        block, full = matmul_lhsT_rhs_row_split(lhs_T[:, m0:m1], rhs, M, matmul=host_matmul)
+        want = lhs_T.T @ rhs_src
+        result[str(M)] = [bool(torch.equal(rhs, rhs_src)), bool(torch.allclose(block, want[m0:m1])),
+                          bool(torch.allclose(full, want)), list(full.shape)]
+        only, none = matmul_lhsT_rhs_row_split(lhs_T[:, m0:m1], rhs, M, matmul=host_matmul, gather=False)
+        assert none is None and torch.allclose(only, want[m0:m1])
+    oks = [None] * world
+    dist.all_gather_object(oks, result)
+    if rank == 0:
+        print(json.dumps(oks))
+    dist.destroy_process_group()
+    """
+)
+
+
+@pytest.mark.parametrize("world,port", [(2, 29641), (3, 29643)])
+def test_row_split_replicates_and_gathers_gloo(tmp_path, world, port):
+    script = tmp_path / "row_split.py"
+    script.write_text(ROW_SPLIT_SCRIPT.format(pkg=str(PKG)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    import json
+
+    per_rank = json.loads([l for l in proc.stdout.splitlines() if l.startswith("[")][-1])
+    assert len(per_rank) == world
+    for res in per_rank:
+        assert res["64"][:3] == [True, True, True] and res["64"][3] == [64, 16]
+        assert res["1000"][:3] == [True, True, True] and res["1000"][3] == [1000, 16]

@@ -1,0 +1,67 @@
+"""Large-M row split over two GPUs: NCCL replication of rhs, local tcgen05 GEMMs, device all-gather.
+
+Needs two GPUs; skipped on a one-GPU box.  The ranks run as child processes under torchrun."""
+
+import json
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+from conftest import PKG
+
+pytestmark = pytest.mark.gpu
+
+SCRIPT = textwrap.dedent(
+    """
+    import sys, json, os
+    sys.path.insert(0, {pkg!r})
+    import torch, torch.distributed as dist
+    from autotune import kernels
+    from autotune.sharded import row_range, replicate, matmul_lhsT_rhs_row_split
+
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    res = {{}}
+    for M, K, N in ((4096, 512, 384), (1000, 264, 136)):   # equal blocks, ragged blocks
+        g = torch.Generator(device="cuda").manual_seed(11)     # same seed: every rank can build the answer
+        lhs_T = (torch.randn(K, M, device="cuda", generator=g) * K ** -0.5).bfloat16()
+        rhs_src = (torch.randn(K, N, device="cuda", generator=g)).bfloat16()
+        rhs = replicate(rhs_src if rank == 0 else None, (K, N), torch.bfloat16, "cuda", src=0)
+        m0, m1 = row_range(M, rank, world)
+        status = kernels.new_status()
+        block, full = matmul_lhsT_rhs_row_split(lhs_T[:, m0:m1], rhs, M)
+        torch.cuda.synchronize()
+        want = lhs_T.float().T @ rhs_src.float()
+        err = ((full.float() - want).abs() / (want.abs() + want.pow(2).mean().sqrt())).max().item()
+        res[str(M)] = [bool(torch.equal(rhs, rhs_src)), err, list(full.shape)]
+    out = [None] * world
+    dist.all_gather_object(out, res)
+    if rank == 0:
+        print(json.dumps(out))
+    dist.destroy_process_group()
+    """
+)
+
+
+def test_row_split_two_gpus_nccl(native_lib, tmp_path):
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "row_split_gpu.py"
+    script.write_text(SCRIPT.format(pkg=str(PKG)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29671", str(script)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ))
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    per_rank = json.loads([l for l in proc.stdout.splitlines() if l.startswith("[")][-1])
+    assert len(per_rank) == 2
+    for r in per_rank:
+        for key, shape in (("4096", [4096, 384]), ("1000", [1000, 136])):
+            same_rhs, err, got_shape = r[key]
+            assert same_rhs and err <= 1e-2 and got_shape == shape
