@@ -189,7 +189,10 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     p.acc_bufs = (2 * acc_cols <= 512) ? 2 : 1;
     p.tmem_cols = next_pow2_cols(acc_cols * p.acc_bufs);
   }
-  if (fam != FAM_RMSNORM) p.smem_bytes = 1024 + p.stages * stage_bytes + ctrl_bytes;
+  if (fam != FAM_RMSNORM) {
+    ctrl_bytes += EPI_STAGE_BYTES;  // output staging of the TMA-store epilogue
+    p.smem_bytes = 1024 + p.stages * stage_bytes + ctrl_bytes;
+  }
   *plan = p;
   if (tmem_need > 512)
     return set_error(B200_ERR_TMEM_OOM, "Out of memory in tmem: accumulator%s need %d of 512 columns",
@@ -251,7 +254,7 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long rows, long col
 }
 
 // ---------------------------------------------------------------------------- launch
-typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
 typedef void (*RmsKernelFn)(const CUtensorMap, const CUtensorMap, const RmsParams);
 
 static GemmKernelFn pick_gemm_kernel(const Plan& p) {
@@ -333,7 +336,7 @@ static size_t skinny_workspace_bytes(long N) {
 struct Prepared {
   GemmKernelFn fn;      // plain GEMM (fam == FAM_LHST)
   RmsKernelFn rms_fn;   // fused kernel (fam == FAM_RMSNORM)
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a, tm_b, tm_out;
   GemmParams gp;
   RmsParams rp;
   SkinnyParams sp;
@@ -443,6 +446,9 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   }
   if (rc) return rc;
   rc = make_tmap_bf16(&pr->tm_b, la.b, la.K, la.N, la.ld_b, 64, plan.tile_k, la.fam == FAM_RMSNORM ? "w" : "rhs");
+  if (rc) return rc;
+  // the epilogue stores 32-row x 64-column boxes; rows and columns past M and N are clipped
+  rc = make_tmap_bf16(&pr->tm_out, la.out, la.M, la.N, la.ld_out, 64, 32, "out");
   if (rc) return rc;
 
   GemmParams& gp = pr->gp;
@@ -566,7 +572,7 @@ static int launch(const Prepared& pr, cudaStream_t stream) {
     return check_cuda(cudaLaunchKernelEx(&lc, rmsnorm_skinny_kernel, pr.tm_b, pr.sp), "skinny RMSNorm GEMM launch");
   if (pr.fused)
     return check_cuda(cudaLaunchKernelEx(&lc, pr.rms_fn, pr.tm_a, pr.tm_b, pr.rp), "fused RMSNorm GEMM launch");
-  return check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.gp), "tcgen05 GEMM launch");
+  return check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.tm_out, pr.gp), "tcgen05 GEMM launch");
 }
 
 }  // namespace b200

@@ -26,6 +26,10 @@ namespace b200 {
 
 constexpr int MAX_STAGES = 12;
 constexpr int GEMM_THREADS = 192;
+// epilogue staging in shared memory: per epilogue warp two buffers of 32 rows x 64 bf16 columns
+// (128-byte rows, 128-byte swizzle), written by the warp and read by its TMA stores
+constexpr int EPI_BUF_BYTES = 32 * 128;
+constexpr int EPI_STAGE_BYTES = 4 * 2 * EPI_BUF_BYTES;
 
 // measurement / test hooks (b200_cfg.reserved[0])
 constexpr int DEBUG_SKIP_PRODUCER = 1;  // producer issues nothing: the consumers' bounded waits run out
@@ -141,7 +145,8 @@ constexpr int A_LHST = 0, A_NORM = 1, A_KMAJOR_PLAIN = 2;
 template <int CTA_GROUP, int M_SUB, int A_MODE = A_LHST>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
-                    const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tm_b,
+                    const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
   constexpr bool NORM = (A_MODE == A_NORM);
   constexpr bool A_KMAJOR = (A_MODE != A_LHST);
   constexpr bool PAIR = (CTA_GROUP == 2);
@@ -165,7 +170,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
   const uint32_t b_base = a_base + stages * a_bytes;
-  const uint32_t ctrl_addr = b_base + stages * b_bytes;
+  const uint32_t out_stage_base = b_base + stages * b_bytes;  // epilogue staging, 1024-byte aligned
+  const uint32_t ctrl_addr = out_stage_base + EPI_STAGE_BYTES;
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (ctrl_addr - smem_u32(smem_raw)));
 
   const int acc_cols = M_SUB * tile_n;
@@ -186,6 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     ctrl->abort_flag = 0;
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(&tm_out);
     for (int s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), 1);
       mbar_init(smem_u32(&ctrl->empty[s]), 1);
@@ -288,7 +295,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (!run_roles) {
     // a CTA that gave up at the grid barrier skips straight to the teardown
   } else if (warp == 0) {
-    if (lane == 0 && p.debug_mode != DEBUG_SKIP_PRODUCER) {
+    // the whole warp runs the loop converged; one elected lane issues each copy and arrival
+    if (p.debug_mode != DEBUG_SKIP_PRODUCER) {
       wctx.role = ROLE_PRODUCER;
       uint32_t it = 0;
       Ring ring;
@@ -303,6 +311,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t s = ring.s;
           const uint32_t ph = ring.ph;
           ok = bounded_wait<false>(wctx, smem_u32(&ctrl->empty[s]), ph ^ 1u, 100 + s, tile, kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint32_t a_s = a_base + s * a_bytes;
           const uint32_t b_s = b_base + s * b_bytes;
@@ -310,34 +319,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t full_local = smem_u32(&ctrl->full[s]);
           if (p.debug_mode == DEBUG_NO_RELOAD && it >= static_cast<uint32_t>(stages)) {
             // measurement aid: operands stay as first loaded, only the barrier protocol runs
-            if (!PAIR || cta_rank == 0) mbar_arrive(full_local);
+            if (!PAIR || cta_rank == 0) mbar_arrive_elect(full_local);
           } else if constexpr (PAIR) {
             const uint32_t full_leader = map_to_cta(full_local, 0);
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_local, 2u * (a_bytes + b_bytes));
+            if (cta_rank == 0) mbar_arrive_expect_tx_elect(full_local, 2u * (a_bytes + b_bytes));
             if constexpr (A_KMAJOR) {
               for (int c = 0; c < tile_k / 64; ++c)
-                tma_load_2d_pair(a_s + c * MC * 128, &tm_a, full_leader, k0 + 64 * c, m_base);
+                tma_load_2d_pair_elect(a_s + c * MC * 128, &tm_a, full_leader, k0 + 64 * c, m_base);
             } else {
               for (int c = 0; c < MC / 64; ++c)
-                tma_load_2d_pair(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
+                tma_load_2d_pair_elect(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
             }
             // B chunks of 64 columns; after this CTA's share of one UMMA the column jumps to the next UMMA
             for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
-              tma_load_2d_pair(b_s + c * tile_k * 128, &tm_b, full_leader, col, k0);
+              tma_load_2d_pair_elect(b_s + c * tile_k * 128, &tm_b, full_leader, col, k0);
               col += 64;
               if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
             }
           } else {
-            mbar_arrive_expect_tx(full_local, a_bytes + b_bytes);
+            mbar_arrive_expect_tx_elect(full_local, a_bytes + b_bytes);
             if constexpr (A_KMAJOR) {
               for (int c = 0; c < tile_k / 64; ++c)
-                tma_load_2d(a_s + c * MC * 128, &tm_a, full_local, k0 + 64 * c, m_base);
+                tma_load_2d_elect(a_s + c * MC * 128, &tm_a, full_local, k0 + 64 * c, m_base);
             } else {
               for (int c = 0; c < MC / 64; ++c)
-                tma_load_2d(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
+                tma_load_2d_elect(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
             }
             for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
-              tma_load_2d(b_s + c * tile_k * 128, &tm_b, full_local, col, k0);
+              tma_load_2d_elect(b_s + c * tile_k * 128, &tm_b, full_local, col, k0);
               col += 64;
               if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
             }
@@ -346,14 +355,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       // tail: every stage released, so no UMMA-completion arrival is still on its way to
       // this CTA's barriers when the CTA exits
-      for (int i = 0; i < stages && ok; ++i, ring.advance(stages))
+      for (int i = 0; i < stages && ok; ++i, ring.advance(stages)) {
         ok = bounded_wait<false>(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1, i);
+        ok = __all_sync(0xffffffffu, ok);
+      }
     }
     __syncwarp();
   }
   // ------------------------------------------------------------------ UMMA issuer
   else if (warp == 1) {
-    if (lane == 0 && cta_rank == 0) {
+    // the whole warp runs the issue loop converged; one elected lane issues each UMMA and commit
+    if (cta_rank == 0) {
       wctx.role = ROLE_MMA;
       const uint32_t idesc =
           make_idesc_bf16_f32(128 * CTA_GROUP, umma_n, A_KMAJOR ? 0 : 1, 1);
@@ -371,12 +383,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
         const uint32_t b = acc.s;
         ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_empty[b]), acc.ph ^ 1u, 200 + b, tile, -1);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * static_cast<uint32_t>(acc_cols);
         for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(stages)) {
           const uint32_t s = ring.s;
           ok = bounded_wait<false>(wctx, smem_u32(&ctrl->full[s]), ring.ph, 300 + s, tile, kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
           uint64_t adesc = a_desc0 + s * a_step;
@@ -395,7 +409,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                                                 (k16 & 3) * 32, 16, 1024);
 #pragma unroll
                 for (int ns = 0; ns < NS; ++ns)
-                  umma_bf16<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n + ns * umma_n), ad,
+                  umma_bf16_elect<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n + ns * umma_n), ad,
                                        bdesc + ns * nsub_step, idesc, (kb | k16) != 0 ? 1u : 0u);
               }
             }
@@ -404,12 +418,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (n_sub == 1) issue_k_block(std::integral_constant<int, 1>{});
             else issue_k_block(std::integral_constant<int, 2>{});
           }
-          if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->empty[s]), 3);
-          else umma_commit_1cta(smem_u32(&ctrl->empty[s]));
+          if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->empty[s]), 3);
+          else umma_commit_1cta_elect(smem_u32(&ctrl->empty[s]));
         }
         if (!ok) break;
-        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->acc_full[b]), 3);
-        else umma_commit_1cta(smem_u32(&ctrl->acc_full[b]));
+        if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->acc_full[b]), 3);
+        else umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[b]));
       }
     }
     __syncwarp();
@@ -418,9 +432,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   else if (warp < 6) {
     wctx.role = ROLE_EPILOGUE;
     const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
-    const int row_in_cta = q * 32 + lane;
     const uint32_t acc_empty_leader =
         PAIR ? map_to_cta(smem_u32(&ctrl->acc_empty[0]), 0) : smem_u32(&ctrl->acc_empty[0]);
+    const uint32_t stage_base = out_stage_base + static_cast<uint32_t>(q) * (2 * EPI_BUF_BYTES);
+    uint32_t sbuf = 0;
     Ring acc;
     bool ok = true;
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
@@ -436,30 +451,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       tc_fence_after();
 #pragma unroll
       for (int mi = 0; mi < M_SUB; ++mi) {
-        const long long grow = static_cast<long long>(m_base) + mi * 128 + row_in_cta;
-        __nv_bfloat16* out_row = p.out + grow * p.ld_out;
+        const int row0 = m_base + mi * 128 + q * 32;  // first of this warp's 32 rows
         float scale = 1.0f;
-        if constexpr (NORM) scale = (grow < p.M) ? __ldcg(p.rinv + grow) : 0.0f;
-        for (int c = 0; c < tile_n / 32; ++c) {
-          uint32_t r[32];
+        if constexpr (NORM) scale = (row0 + lane < p.M) ? __ldcg(p.rinv + row0 + lane) : 0.0f;
+        for (int c = 0; c < tile_n / 64; ++c) {
+          // 64 accumulator columns of this lane's row -> bf16 -> one 128-byte row of the staging
+          // buffer (16-byte chunk j lands at chunk j ^ (row & 7): the 128-byte swizzle the store's
+          // tensor map undoes, and conflict-free for the warp's 16-byte shared stores)
+          uint32_t r0[32], r1[32];
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                 static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 32);
-          tmem_ld_32x32b_x32(taddr, r);
+                                 static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 64);
+          tmem_ld_32x32b_x32(taddr, r0);
+          tmem_ld_32x32b_x32(taddr + 32u, r1);
           tmem_ld_wait();
-          if (grow < p.M) {
-            const int col0 = n_base + c * 32;
+          const int col0 = n_base + c * 64;
+          if (row0 < p.M && col0 < p.N) {  // warp-uniform; rows / columns past the edge are clipped by the store
+            const uint32_t buf = stage_base + sbuf * EPI_BUF_BYTES;
+            if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer has drained it
+            __syncwarp();
+            const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+            const uint32_t sw = static_cast<uint32_t>(lane & 7);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = col0 + g * 8;
-              if (col + 8 <= p.N) {
-                uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * scale, __uint_as_float(r[g * 8 + 1]) * scale);
-                v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * scale, __uint_as_float(r[g * 8 + 3]) * scale);
-                v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * scale, __uint_as_float(r[g * 8 + 5]) * scale);
-                v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * scale, __uint_as_float(r[g * 8 + 7]) * scale);
-                *reinterpret_cast<uint4*>(out_row + col) = v;
-              }
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t* r = (j < 4) ? (r0 + j * 8) : (r1 + (j - 4) * 8);
+              st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4),
+                           pack_bf16x2(__uint_as_float(r[0]) * scale, __uint_as_float(r[1]) * scale),
+                           pack_bf16x2(__uint_as_float(r[2]) * scale, __uint_as_float(r[3]) * scale),
+                           pack_bf16x2(__uint_as_float(r[4]) * scale, __uint_as_float(r[5]) * scale),
+                           pack_bf16x2(__uint_as_float(r[6]) * scale, __uint_as_float(r[7]) * scale));
             }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tm_out, buf, col0, row0);
+              tma_store_commit();
+            }
+            sbuf ^= 1u;
           }
         }
       }
@@ -470,6 +497,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         else mbar_arrive(acc_empty_leader + b * 8);
       }
     }
+    if (lane == 0) tma_store_wait_all<0>();  // staging buffers are read out and the rows written before exit
   }
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
