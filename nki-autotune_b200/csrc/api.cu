@@ -387,7 +387,7 @@ static int prepare_skinny(const LaunchArgs& la, const b200_cfg* cfg, const Plan&
   pr->smem = static_cast<size_t>(plan.smem_bytes);
   pr->block = dim3(SKINNY_THREADS);
   rc = check_cuda(cudaFuncSetAttribute(reinterpret_cast<const void*>(rmsnorm_skinny_kernel),
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pr->smem)),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BUDGET)),
                   "cudaFuncSetAttribute(max dynamic shared memory)");
   if (rc) return rc;
   long long units = static_cast<long long>(sp.num_n_tiles) * sp.num_k_blocks;
@@ -518,8 +518,10 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   pr->smem = static_cast<size_t>(plan.smem_bytes);
   pr->block = dim3(static_cast<unsigned>(fused ? RMS_THREADS : GEMM_THREADS));
   const void* kernel_ptr = fused ? reinterpret_cast<const void*>(pr->rms_fn) : reinterpret_cast<const void*>(pr->fn);
+  // always the whole budget: the attribute is sticky per function, and a replayed (cached) launch
+  // of a larger configuration must not find it lowered by a smaller one prepared in between
   rc = check_cuda(cudaFuncSetAttribute(kernel_ptr, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(pr->smem)),
+                                       static_cast<int>(SMEM_BUDGET)),
                   "cudaFuncSetAttribute(max dynamic shared memory)");
   if (rc) return rc;
 
@@ -551,6 +553,46 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (getenv("B200_AUTOTUNE_DEBUG") != nullptr)
     fprintf(stderr, "[b200] %d SMs, cluster %d, CTA groups %ld (work units %ld), grid %u, block %u, smem %zu\n",
             di.sm_count, plan.cluster, groups, units, pr->grid.x, pr->block.x, pr->smem);
+  return B200_OK;
+}
+
+// Replay cache: the entry points are called once per step with the same buffers, shapes and
+// candidate, so the last few prepared launches are kept per host thread (tensor-map encoding,
+// the occupancy query and the attribute call cost far more host time than the launch itself).
+struct PrepKey {
+  LaunchArgs la;
+  b200_cfg cfg;
+  int has_cfg;
+  int device;
+  int* dev_status;
+};
+
+static int prepare_cached(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, Prepared* pr) {
+  constexpr int SLOTS = 8;
+  struct Slot { bool used; PrepKey key; Prepared pr; };
+  static thread_local Slot slots[SLOTS];
+  static thread_local int next_slot = 0;
+  PrepKey key;
+  memset(&key, 0, sizeof(key));  // padding bytes too: keys are compared with memcmp
+  key.la.fam = la.fam; key.la.a = la.a; key.la.b = la.b; key.la.gamma = la.gamma; key.la.out = la.out;
+  key.la.M = la.M; key.la.N = la.N; key.la.K = la.K;
+  key.la.ld_a = la.ld_a; key.la.ld_b = la.ld_b; key.la.ld_out = la.ld_out;
+  key.la.eps = la.eps; key.la.workspace = la.workspace; key.la.workspace_bytes = la.workspace_bytes;
+  if (cfg) { memcpy(&key.cfg, cfg, sizeof(b200_cfg)); key.has_cfg = 1; }
+  key.dev_status = dev_status;
+  if (cudaGetDevice(&key.device) != cudaSuccess) { (void)cudaGetLastError(); key.device = -1; }
+  for (int i = 0; i < SLOTS; ++i)
+    if (slots[i].used && memcmp(&slots[i].key, &key, sizeof(key)) == 0) {
+      *pr = slots[i].pr;
+      return B200_OK;
+    }
+  int rc = prepare(la, cfg, dev_status, pr);
+  if (rc) return rc;
+  Slot& s = slots[next_slot];
+  next_slot = (next_slot + 1) % SLOTS;
+  s.used = true;
+  s.key = key;
+  s.pr = *pr;
   return B200_OK;
 }
 
@@ -618,7 +660,7 @@ extern "C" int b200_matmul_lhsT_rhs(const void* lhsT, const void* rhs, void* out
   LaunchArgs la{FAM_LHST, lhsT, rhs, nullptr, out, M, N, K, ld_lhsT ? ld_lhsT : M, ld_rhs ? ld_rhs : N,
                 ld_out ? ld_out : N, 0.0f, workspace, workspace_bytes};
   Prepared pr;
-  int rc = prepare(la, cfg, dev_status, &pr);
+  int rc = prepare_cached(la, cfg, dev_status, &pr);
   if (rc) return rc;
   return launch(pr, static_cast<cudaStream_t>(stream));
 }
@@ -629,7 +671,7 @@ extern "C" int b200_matmul_lhs_rhs(const void* lhs, const void* rhs, void* out, 
   LaunchArgs la{FAM_LHS, lhs, rhs, nullptr, out, M, N, K, ld_lhs ? ld_lhs : K, ld_rhs ? ld_rhs : N,
                 ld_out ? ld_out : N, 0.0f, workspace, workspace_bytes};
   Prepared pr;
-  int rc = prepare(la, cfg, dev_status, &pr);
+  int rc = prepare_cached(la, cfg, dev_status, &pr);
   if (rc) return rc;
   return launch(pr, static_cast<cudaStream_t>(stream));
 }
@@ -639,7 +681,7 @@ extern "C" int b200_rmsnorm_matmul(const void* x, const void* gamma, const void*
                                    int* dev_status, void* stream) {
   LaunchArgs la{FAM_RMSNORM, x, w, gamma, out, M, N, K, K, N, N, eps, workspace, workspace_bytes};
   Prepared pr;
-  int rc = prepare(la, cfg, dev_status, &pr);
+  int rc = prepare_cached(la, cfg, dev_status, &pr);
   if (rc) return rc;
   return launch(pr, static_cast<cudaStream_t>(stream));
 }

@@ -132,30 +132,36 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   SkinnyWait wctx{ctrl, p.status, p.timeout_cycles, 0};
 
   // ------------------------------------------------------------------ TMA producer (w tiles)
+  // producer and issuer loops run with all lanes converged; one elected lane issues each copy,
+  // UMMA and commit (loop state and descriptors stay in uniform registers)
   if (warp == 0) {
-    if (lane == 0) {
+    {
       wctx.role = ROLE_PRODUCER;
       Ring ring;
       bool ok = true;
+      int nt = static_cast<int>(u_begin / nkb);
+      int kb = static_cast<int>(u_begin - static_cast<long long>(nt) * nkb);
       for (long long u = u_begin; u < u_end && ok; ++u, ring.advance(stages)) {
-        const int nt = static_cast<int>(u / nkb);
-        const int kb = static_cast<int>(u - static_cast<long long>(nt) * nkb);
         ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 100 + ring.s, static_cast<int>(u - u_begin));
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint32_t w_s = w_base + ring.s * w_bytes;
         const uint32_t fw = smem_u32(&ctrl->full_w[ring.s]);
-        mbar_arrive_expect_tx(fw, w_bytes);
+        mbar_arrive_expect_tx_elect(fw, w_bytes);
         for (int c = 0; c < SKINNY_TILE_N / 64; ++c)
-          tma_load_2d(w_s + c * tile_k * 128, &tm_w, fw, nt * SKINNY_TILE_N + 64 * c, kb * tile_k);
+          tma_load_2d_elect(w_s + c * tile_k * 128, &tm_w, fw, nt * SKINNY_TILE_N + 64 * c, kb * tile_k);
+        if (++kb == nkb) { kb = 0; ++nt; }
       }
-      for (int i = 0; i < stages && ok; ++i, ring.advance(stages))
+      for (int i = 0; i < stages && ok; ++i, ring.advance(stages)) {
         ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1);
+        ok = __all_sync(0xffffffffu, ok);
+      }
     }
     __syncwarp();
   }
   // ------------------------------------------------------------------ UMMA issuer
   else if (warp == 1) {
-    if (lane == 0) {
+    {
       wctx.role = ROLE_MMA;
       const uint32_t idesc = make_idesc_bf16_f32(128, SKINNY_TILE_N, 0, 1);  // A K-major, B MN-major
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
@@ -168,6 +174,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         const int nt = static_cast<int>(u / nkb);
         const long long seg_end = min(u_end, static_cast<long long>(nt + 1) * nkb);
         ok = skinny_wait(wctx, smem_u32(&ctrl->acc_empty[acc.s]), acc.ph ^ 1u, 200 + acc.s, static_cast<int>(u - u_begin));
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc.s * SKINNY_TILE_N;
@@ -175,7 +182,9 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         for (; u < seg_end; ++u, ring.advance(stages)) {
           const uint32_t s = ring.s;
           ok = skinny_wait(wctx, smem_u32(&ctrl->full_w[s]), ring.ph, 300 + s, static_cast<int>(u - u_begin));
+          ok = __all_sync(0xffffffffu, ok);
           if (ok) ok = skinny_wait(wctx, smem_u32(&ctrl->full_x[s]), ring.ph, 400 + s, static_cast<int>(u - u_begin));
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
           uint64_t bdesc = b_desc0 + s * (w_bytes >> 4);
@@ -183,13 +192,13 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
           for (int k16 = 0; k16 < nk16; ++k16, bdesc += 128) {
             const uint64_t adesc =
                 make_smem_desc_sw128(x_s + (k16 >> 2) * (SKINNY_ROWS * 128) + (k16 & 3) * 32, 16, 1024);
-            umma_bf16<1>(d_tmem, adesc, bdesc, idesc, first ? 0u : 1u);
+            umma_bf16_elect<1>(d_tmem, adesc, bdesc, idesc, first ? 0u : 1u);
             first = false;
           }
-          umma_commit_1cta(smem_u32(&ctrl->empty[s]));
+          umma_commit_1cta_elect(smem_u32(&ctrl->empty[s]));
         }
         if (!ok) break;
-        umma_commit_1cta(smem_u32(&ctrl->acc_full[acc.s]));
+        umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[acc.s]));
         acc.advance(SKINNY_ACC_BUFS);
       }
     }

@@ -197,8 +197,10 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
   // ------------------------------------------------------------------ TMA producer, w tiles
   // The x and w rings advance independently (separate producer warps, separate barriers), so
   // the transform of later x tiles runs ahead while earlier w tiles are still being consumed.
+  // The producer and issuer warps run their loops with all lanes converged; one elected lane
+  // issues each copy, UMMA and commit, so loop state and descriptors stay in uniform registers.
   if (warp == 0) {
-    if (lane == 0) {
+    {
       wctx.role = ROLE_PRODUCER;
       Ring ring;
       bool ok = true;
@@ -209,30 +211,33 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(stages)) {
           const uint32_t s = ring.s;
           ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[s]), ring.ph ^ 1u, 100 + s, tile, kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint32_t b_s = b_base + s * b_bytes;
           const int k0 = kb * tile_k;
           const uint32_t fb = smem_u32(&ctrl->full_b[s]);
           if constexpr (PAIR) {
             const uint32_t fb_leader = map_to_cta(fb, 0);
-            if (cta_rank == 0) mbar_arrive_expect_tx(fb, 2u * b_bytes);
+            if (cta_rank == 0) mbar_arrive_expect_tx_elect(fb, 2u * b_bytes);
             for (int c = 0; c < nc / 64; ++c)
-              tma_load_2d_pair(b_s + c * tile_k * 128, &tm_w, fb_leader, n_base + 64 * c, k0);
+              tma_load_2d_pair_elect(b_s + c * tile_k * 128, &tm_w, fb_leader, n_base + 64 * c, k0);
           } else {
-            mbar_arrive_expect_tx(fb, b_bytes);
+            mbar_arrive_expect_tx_elect(fb, b_bytes);
             for (int c = 0; c < nc / 64; ++c)
-              tma_load_2d(b_s + c * tile_k * 128, &tm_w, fb, n_base + 64 * c, k0);
+              tma_load_2d_elect(b_s + c * tile_k * 128, &tm_w, fb, n_base + 64 * c, k0);
           }
         }
       }
-      for (int i = 0; i < stages && ok; ++i, ring.advance(stages))  // tail: all stages released
+      for (int i = 0; i < stages && ok; ++i, ring.advance(stages)) {  // tail: all stages released
         ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_b[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1, i);
+        ok = __all_sync(0xffffffffu, ok);
+      }
     }
     __syncwarp();
   }
   // ------------------------------------------------------------------ TMA producer, x tiles
   else if (warp == RMS_A_PRODUCER_WARP) {
-    if (lane == 0) {
+    {
       wctx.role = ROLE_PRODUCER;
       Ring ring;
       bool ok = true;
@@ -243,23 +248,26 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(a_stages)) {
           const uint32_t s = ring.s;
           ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[s]), ring.ph ^ 1u, 120 + s, tile, kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint32_t a_s = a_base + s * a_bytes;
           const int k0 = kb * tile_k;
           const uint32_t fa = smem_u32(&ctrl->full_a[s]);
-          mbar_arrive_expect_tx(fa, a_bytes);
+          mbar_arrive_expect_tx_elect(fa, a_bytes);
           for (int c = 0; c < tile_k / 64; ++c)
-            tma_load_2d(a_s + c * MC * 128, &tm_x, fa, k0 + 64 * c, m_base);
+            tma_load_2d_elect(a_s + c * MC * 128, &tm_x, fa, k0 + 64 * c, m_base);
         }
       }
-      for (int i = 0; i < a_stages && ok; ++i, ring.advance(a_stages))
+      for (int i = 0; i < a_stages && ok; ++i, ring.advance(a_stages)) {
         ok = rms_wait<false>(wctx, smem_u32(&ctrl->empty_a[ring.s]), ring.ph ^ 1u, 170 + ring.s, -1, i);
+        ok = __all_sync(0xffffffffu, ok);
+      }
     }
     __syncwarp();
   }
   // ------------------------------------------------------------------ UMMA issuer
   else if (warp == 1) {
-    if (lane == 0 && cta_rank == 0) {
+    if (cta_rank == 0) {
       wctx.role = ROLE_MMA;
       const uint32_t idesc = make_idesc_bf16_f32(128 * CTA_GROUP, tile_n, 0, 1);
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
@@ -271,6 +279,7 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
         const uint32_t b = acc.s;
         ok = rms_wait<false>(wctx, smem_u32(&ctrl->acc_empty[b]), acc.ph ^ 1u, 200 + b, tile, -1);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * static_cast<uint32_t>(acc_cols);
@@ -278,7 +287,9 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
           const uint32_t s = ring.s;
           const uint32_t ta = slot.s;
           ok = rms_wait<false>(wctx, smem_u32(&ctrl->full_b[s]), ring.ph, 300 + s, tile, kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (ok) ok = rms_wait<false>(wctx, smem_u32(&ctrl->a_ready[ta]), slot.ph, 400 + ta, tile, kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
           uint64_t bdesc = b_desc0 + s * b_step;
@@ -288,21 +299,21 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
 #pragma unroll
             for (int mi = 0; mi < M_SUB; ++mi)
               if (p.debug_mode != DEBUG_NO_MMA)
-                umma_bf16_ts<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n),
+                umma_bf16_ts_elect<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n),
                                       a_tmem + static_cast<uint32_t>(mi * (tile_k / 2)), bdesc, idesc,
                                       (kb | k16) != 0 ? 1u : 0u);
           }
           if constexpr (PAIR) {
-            umma_commit_pair(smem_u32(&ctrl->empty_b[s]), 3);
-            umma_commit_pair(smem_u32(&ctrl->a_free[ta]), 3);
+            umma_commit_pair_elect(smem_u32(&ctrl->empty_b[s]), 3);
+            umma_commit_pair_elect(smem_u32(&ctrl->a_free[ta]), 3);
           } else {
-            umma_commit_1cta(smem_u32(&ctrl->empty_b[s]));
-            umma_commit_1cta(smem_u32(&ctrl->a_free[ta]));
+            umma_commit_1cta_elect(smem_u32(&ctrl->empty_b[s]));
+            umma_commit_1cta_elect(smem_u32(&ctrl->a_free[ta]));
           }
         }
         if (!ok) break;
-        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->acc_full[b]), 3);
-        else umma_commit_1cta(smem_u32(&ctrl->acc_full[b]));
+        if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->acc_full[b]), 3);
+        else umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[b]));
       }
     }
     __syncwarp();
