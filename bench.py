@@ -528,10 +528,17 @@ def run_extras(ranks: Ranks, torch, kernels, args) -> dict:
         fails = ranks.gather(len(res.failures))
         if ranks.rank == 0:
             flat = sorted((r for part in rows for r in part), key=lambda r: r[1])
-            extras["sweep_64_candidates_8192"] = {
+            row = {
                 "wallclock_s": round(wall, 2), "n_gpus": ranks.world, "succeeded": len(flat), "failed": sum(fails),
                 "best": flat[0] if flat else None,
             }
+            if ranks.world > 1 and flat:
+                # the leaders were timed on different GPUs: time the top three again on this one
+                top = {name: jobs[name] for name, _, _ in flat[:3]}
+                again = profile(top, "", 1, "b200", False, warmup=2, iters=5, n_gpus=1)
+                row["top3_retimed_on_rank0"] = sorted(
+                    ((r.kernel_name, r.total_time_s, r.mfu) for r in again.successes), key=lambda r: r[1])
+            extras["sweep_64_candidates_8192"] = row
     return extras
 
 

@@ -1,6 +1,6 @@
 """Sweep the meta-parameter grid of ``matmul_lhsT_rhs`` on the GPUs of this box.
 
-    python examples/tune_matmul_lhsT_rhs.py --cache DIR [--detailed] [--size 8192] [--gpus N]
+    python examples/tune_matmul_lhsT_rhs.py --cache DIR [--detailed] [--size 8192] [--gpus N] [--extended]
 
 Counterpart of ``examples/tune_matmul_lhsT_rhs.py`` upstream: build the jobs, profile them
 (every candidate is checked against the fp32 device kernel before it is accepted), print the
@@ -17,7 +17,7 @@ sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "nki-autotune_b2
 
 from autotune.runner.api import profile  # noqa: E402
 from autotune.runner.baseline import profile_numpy_baseline  # noqa: E402
-from autotune.runner.candidate import enumerate_grid, jobs_from_candidates  # noqa: E402
+from autotune.runner.candidate import enumerate_grid, extended_grid, jobs_from_candidates  # noqa: E402
 from autotune.runner.types import profiler_percent  # noqa: E402
 
 SEED = 1
@@ -29,6 +29,9 @@ def main() -> None:
     ap.add_argument("--detailed", action="store_true", help="keep the per-launch timings of every candidate")
     ap.add_argument("--size", type=int, default=8192, help="K = M = N")
     ap.add_argument("--gpus", type=int, default=None, help="shard the candidates over this many GPUs")
+    ap.add_argument("--retime-top", type=int, default=5,
+                    help="after a multi-GPU sweep, time the fastest N candidates again on one GPU")
+    ap.add_argument("--extended", action="store_true", help="add the 24 large-tile points (512-row / 512-column tiles)")
     args = ap.parse_args()
 
     n = args.size
@@ -37,10 +40,11 @@ def main() -> None:
     cache_dir = os.path.join(args.cache, "tune_matmul_lhsT_rhs")
     shutil.rmtree(cache_dir, ignore_errors=True)
 
-    jobs = jobs_from_candidates(enumerate_grid("matmul_lhsT_rhs"), (n, n), specs)
+    grid = extended_grid("matmul_lhsT_rhs") if args.extended else enumerate_grid("matmul_lhsT_rhs")
+    jobs = jobs_from_candidates(grid, (n, n), specs)
     print(f"[tune] profiling {len(jobs)} candidates at {n}^3 ...\n")
     output = profile(jobs, cache_dir=cache_dir, seed=SEED, neuron_platform_target="b200",
-                     collect_detailed_profile=args.detailed, n_gpus=args.gpus)
+                     collect_detailed_profile=args.detailed, n_gpus=args.gpus, retime_top=args.retime_top)
     print(output)
 
     baseline, how = profile_numpy_baseline(lambda lhs_T, rhs: lhs_T.T @ rhs, specs,

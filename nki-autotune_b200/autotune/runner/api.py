@@ -30,6 +30,7 @@ def profile(
     warmup: int = 3,
     iters: int = 10,
     shard: tuple[int, int] | None = None,
+    retime_top: int = 0,
 ) -> ProfileOutput:
     """Validate and time a set of candidates on the GPUs of this box.
 
@@ -46,6 +47,8 @@ def profile(
         warmup, iters: Untimed and timed launches per candidate (extension).
         shard: ``(rank, world)`` when the caller already runs one process per GPU; this
             process then times only its share of the candidates (extension).
+        retime_top: After a sweep sharded over several GPUs, time the fastest ``retime_top``
+            candidates again on one GPU so that the leaders are ranked on one device (extension).
 
     Returns:
         ``ProfileOutput`` with every candidate present, as a success or as a failure row.
@@ -68,6 +71,7 @@ def profile(
         warmup=warmup,
         iters=iters,
         shard=shard,
+        retime_top=retime_top,
     )
     elapsed_s = time.monotonic() - start
     logger.info("Profile complete: %d results in %.1fs", len(results), elapsed_s)

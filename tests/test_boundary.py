@@ -7,7 +7,7 @@ import re
 import numpy as np
 import pytest
 
-from autotune.runner.candidate import Candidate, enumerate_grid, jobs_from_candidates, parse_source
+from autotune.runner.candidate import Candidate, enumerate_grid, extended_grid, jobs_from_candidates, parse_source
 from autotune.runner.output import ProfileOutput, write_kernel_sources, write_results_json
 from autotune.runner.types import KernelJob, ProfileResult, make_failure, profiler_percent, resolve_dtype, tensor_inputs
 
@@ -99,6 +99,8 @@ def test_candidate_round_trip_and_grid():
     assert parse_source(Candidate("matmul_lhs_rhs", {"tile_m": 128, "norm_mode": 2}).to_source()).config["norm_mode"] == 2
     grid = enumerate_grid("matmul_lhsT_rhs")
     assert len(grid) == 64 and len({tuple(sorted(g.config.items())) for g in grid}) == 64
+    ext = extended_grid("matmul_lhsT_rhs")
+    assert len(ext) == 88 and ext[:64] == grid and len({tuple(sorted(g.config.items())) for g in ext}) == 88
     with pytest.raises(ValueError):
         parse_source("FAMILY = 'nope'\n")
     with pytest.raises(ValueError):
@@ -137,6 +139,9 @@ def test_cfg_check_budgets(native_lib):
     accepted = sum(native.cfg_check("matmul_lhsT_rhs", c.config, 8192, 8192, 8192)[0] == native.OK
                    for c in enumerate_grid("matmul_lhsT_rhs"))
     assert 0 < accepted < 64  # the grid holds both runnable and over-subscribed points
+    big = [native.cfg_check("matmul_lhsT_rhs", c.config, 8192, 8192, 8192)[0] for c in extended_grid("matmul_lhsT_rhs")[64:]]
+    assert native.OK in big and native.ERR_SMEM_OOM in big and set(big) <= {native.OK, native.ERR_SMEM_OOM}
+    print("accepted of the 64-point grid:", accepted, "of the 24 large-tile points:", big.count(native.OK))
 
 
 def test_cfg_check_families_and_scratch_sizes(native_lib):

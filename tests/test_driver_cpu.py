@@ -35,6 +35,23 @@ def test_pool_gathers_all_results_and_pins_devices():
     assert env_of["k_0.py"] == "0" and env_of["k_1.py"] == "1" and env_of["k_5.py"] == "2" and env_of["k_3.py"] == "0"
 
 
+def test_top_k_is_timed_again_on_one_device():
+    from autotune.runner.driver import retime_top_k
+
+    items = _items(6)
+    first = run_sharded(shard_round_robin(items, 3), fake_workers.well_behaved, {}, ["0", "1", "2"], deadline_s=30, startup_s=60)
+    # candidate k_i "takes" (1 + i) ms in the fake worker; the three fastest are k_0, k_1, k_2
+    out = retime_top_k(first, items, 3, {}, "5", 30, worker=fake_workers.well_behaved, startup_s=60)
+    assert sorted(r.kernel_name for r in out) == sorted(r.kernel_name for r in first)
+    by = {r.kernel_name: r.profiler_summary for r in out}
+    for name in ("k_0.py", "k_1.py", "k_2.py"):
+        assert by[name]["retimed_on_one_gpu"] and by[name]["device_env"] == "5"
+        assert by[name]["first_pass_total_time"] == by[name]["total_time"]          # the fake is deterministic
+    for name in ("k_3.py", "k_4.py", "k_5.py"):
+        assert "retimed_on_one_gpu" not in by[name] and by[name]["device_env"] in ("0", "1", "2")
+    assert retime_top_k(first, items, 0, {}, "5", 30, worker=fake_workers.well_behaved) == first
+
+
 @pytest.mark.parametrize("kind,needle", [("raise", "injected failure"), ("exit", "died"), ("hang", "deadline")])
 def test_one_bad_candidate_costs_one_row(kind, needle):
     items = _items(6, **{"k_2.py": kind})
