@@ -129,7 +129,10 @@ def _footer_lines(rows: list[SuccessRow], out: ProfileOutput) -> list[str]:
     lines = ["\nSummary:", f"  Succeeded:  {len(rows)}/{len(out.results)}", f"  Wallclock:  {out.elapsed_s:.1f}s"]
     if rows:
         times = [r.total_time_s for r in rows]
-        lines.append(f"  Best:       {min(times):.6f} s ({rows[0].kernel_name})")
+        # upstream prints the first row's name next to the minimum (output.py:136); the name
+        # printed here is the one the minimum belongs to
+        best = min(rows, key=lambda r: r.total_time_s)
+        lines.append(f"  Best:       {best.total_time_s:.6f} s ({best.kernel_name})")
         lines.append(f"  Worst:      {max(times):.6f} s")
     if out.cache_dir:
         lines.append(f"  Cache:      {out.cache_dir}")
