@@ -130,12 +130,13 @@ int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* o
 /* The M <= 16 case of b200_rmsnorm_matmul for callers that cannot allocate device memory at the
  * call site (an engine that has handed the whole device heap to its own pools, a thread that
  * must stay out of the allocator's locks): the kernel's scratch lives in a static device array
- * inside the library (16 x B200_NOALLOC_MAX_N floats + counters, about 2 MB, held by every GPU
- * that loads the library until the process exits) instead of a caller workspace.  No cudaMalloc,
+ * inside the library (one 16 x 256 fp32 partial tile per 256-column tile and per CTA at
+ * B200_NOALLOC_MAX_N, plus counters: about 4.7 MB, held by every GPU that loads the library until
+ * the process exits) instead of a caller workspace.  No cudaMalloc,
  * cudaFree or other allocating call is made.  Requires 1 <= M <= 16 and N <= B200_NOALLOC_MAX_N
  * (otherwise B200_ERR_BAD_SHAPE).  The first call on each device resolves the array's device
  * address; make that call outside any stream capture.  All calls on a device share the one
- * array: each call clears the part it uses on `stream` first, and two calls that can overlap
+ * array: each call clears the counters it uses on `stream` first, and two calls that can overlap
  * on the GPU (different streams without ordering) race and give wrong results.
  * No counterpart in the reference. */
 int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, const void* w, void* out,

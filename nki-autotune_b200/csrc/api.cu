@@ -327,9 +327,15 @@ static size_t prologue_workspace_bytes(long M, long K) {
   return align256(static_cast<size_t>(M) * K * 2) + align256(static_cast<size_t>(M) * sizeof(float)) + 256;
 }
 
+// skinny kernel: [tile counters: one int per 256-column tile, zero between launches]
+//                [partial-tile slots: (tiles + SKINNY_MAX_CTAS) x [16][256] fp32, written before read]
+static size_t skinny_counter_bytes(long N) {
+  const size_t tiles = static_cast<size_t>((N + SKINNY_TILE_N - 1) / SKINNY_TILE_N);
+  return align256(tiles * sizeof(int));
+}
 static size_t skinny_workspace_bytes(long N) {
   const size_t tiles = static_cast<size_t>((N + SKINNY_TILE_N - 1) / SKINNY_TILE_N);
-  return ((static_cast<size_t>(SKINNY_ROWS) * N * sizeof(float) + tiles * sizeof(int)) + 255) & ~static_cast<size_t>(255);
+  return skinny_counter_bytes(N) + (tiles + SKINNY_MAX_CTAS) * SKINNY_SLOT_FLOATS * sizeof(float);
 }
 
 // A prepared launch: tensor maps and parameters are built once and can be replayed.
@@ -373,8 +379,8 @@ static int prepare_skinny(const LaunchArgs& la, const b200_cfg* cfg, const Plan&
   sp.x = static_cast<const __nv_bfloat16*>(la.a);
   sp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
   sp.out = static_cast<__nv_bfloat16*>(la.out);
-  sp.scratch = static_cast<float*>(la.workspace);
-  sp.tile_count = reinterpret_cast<int*>(sp.scratch + static_cast<size_t>(SKINNY_ROWS) * la.N);
+  sp.tile_count = static_cast<int*>(la.workspace);
+  sp.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(la.workspace) + skinny_counter_bytes(la.N));
   sp.eps = la.eps;
   sp.inv_k = 1.0f / static_cast<float>(la.K);
   sp.status = dev_status;
@@ -392,6 +398,7 @@ static int prepare_skinny(const LaunchArgs& la, const b200_cfg* cfg, const Plan&
   if (rc) return rc;
   long long units = static_cast<long long>(sp.num_n_tiles) * sp.num_k_blocks;
   long long grid = di.sm_count;
+  if (grid > SKINNY_MAX_CTAS) grid = SKINNY_MAX_CTAS;  // the scratch holds one slot per tile and per CTA
   if (grid > units) grid = units;
   pr->grid = dim3(static_cast<unsigned>(grid));
   return B200_OK;
@@ -748,8 +755,11 @@ extern "C" int b200_time_kernel(const b200_problem* p, const b200_cfg* cfg, void
 // library's device image: it costs NOALLOC_SCRATCH_BYTES on every GPU that loads the library,
 // for the life of the process, and it caps N at B200_NOALLOC_MAX_N.
 namespace b200 {
-constexpr size_t NOALLOC_SCRATCH_BYTES =
-    static_cast<size_t>(SKINNY_ROWS) * B200_NOALLOC_MAX_N * sizeof(float) + 4096;  // sums + tile counters
+// tile counters + one partial-tile slot per tile and per CTA at the largest N served
+// (the same layout skinny_workspace_bytes describes)
+constexpr size_t NOALLOC_TILES = B200_NOALLOC_MAX_N / SKINNY_TILE_N;
+constexpr size_t NOALLOC_SCRATCH_BYTES = ((NOALLOC_TILES * sizeof(int) + 255) / 256) * 256 +
+                                         (NOALLOC_TILES + SKINNY_MAX_CTAS) * SKINNY_SLOT_FLOATS * sizeof(float);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
 // Device address of the array, per device ordinal.  The symbol name above is only a host-side
 // handle: it must be turned into an address with cudaGetSymbolAddress while that device is current.
@@ -784,9 +794,11 @@ extern "C" int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, con
     g_noalloc_addr[dev] = addr;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  // The array keeps whatever the previous call (or an aborted one) left: the partial sums and the
-  // tile counters must start at zero, so the part this call uses is cleared on the same stream.
-  rc = check_cuda(cudaMemsetAsync(g_noalloc_addr[dev], 0, need, stream), "clearing the built-in scratch");
+  // The array keeps whatever the previous call (or an aborted one) left.  Only the tile counters
+  // must start at zero (partial tiles are written before they are read), so they are cleared on
+  // the same stream.
+  rc = check_cuda(cudaMemsetAsync(g_noalloc_addr[dev], 0, skinny_counter_bytes(N), stream),
+                  "clearing the counters of the built-in scratch");
   if (rc) return rc;
   LaunchArgs la{FAM_RMSNORM, x, w, gamma, out, M, N, K, K, N, N, eps, g_noalloc_addr[dev], NOALLOC_SCRATCH_BYTES};
   Prepared pr;

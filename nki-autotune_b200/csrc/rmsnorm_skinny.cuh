@@ -27,6 +27,8 @@ constexpr int SKINNY_TILE_N = 256;    // weight columns per tile (UMMA N): 512 c
 constexpr int SKINNY_ACC_BUFS = 2;    // 256-column accumulators in tensor memory
 constexpr int SKINNY_TMEM_COLS = SKINNY_ACC_BUFS * SKINNY_TILE_N;
 constexpr int SKINNY_THREADS = 32 * 10;
+constexpr int SKINNY_MAX_CTAS = 160;  // grid cap: bounds the number of partial-tile slots in the scratch
+constexpr int SKINNY_SLOT_FLOATS = SKINNY_ROWS * SKINNY_TILE_N;  // one partial tile, [16][256] fp32
 
 struct SkinnyParams {
   int M, N, K;
@@ -35,8 +37,8 @@ struct SkinnyParams {
   const __nv_bfloat16* x;
   const __nv_bfloat16* gamma;   // may be nullptr
   __nv_bfloat16* out;
-  float* scratch;               // [16][N] fp32 partial sums, all zero between launches
-  int* tile_count;              // [num_n_tiles] contributions seen, all zero between launches
+  float* partial;               // [num_n_tiles + gridDim.x][16][256] fp32 partial tiles, written before read
+  int* tile_count;              // [num_n_tiles] k-blocks contributed so far, all zero between launches
   float eps, inv_k;
   int* status;
   long long timeout_cycles;
@@ -51,6 +53,9 @@ struct alignas(16) SkinnyCtrl {
   uint32_t tmem_base;
   volatile int abort_flag;
   float rinv[SKINNY_ROWS];
+  // drain staging: 16 rows x 32 fp32 columns, rows padded to 144 bytes so that both the row-wise
+  // writes and the transposed reads are free of bank conflicts
+  alignas(16) float xpose[SKINNY_ROWS][36];
 };
 
 struct SkinnyWait {
@@ -254,29 +259,42 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       tc_fence_after();
       const int n0 = nt * SKINNY_TILE_N;
       const bool whole_k = (seg_blocks == nkb);  // this CTA summed the tile's whole K range
-      const float my_rinv = ctrl->rinv[lane & 15];
+      // Lane m holds row m of the accumulator, 32 columns per load.  Storing that way would put 16
+      // different rows in every store instruction (16-byte pieces of 16 lines), which the memory
+      // pipe takes one piece at a time; the chunk is transposed through shared memory instead so
+      // that eight lanes cover one row's 128 bytes and an instruction writes four whole lines.
+      const int t_row = lane >> 3, t_chunk = lane & 7;  // transposed view: 4 rows x 8 chunks per pass
+      float* const slot = p.partial + static_cast<size_t>(blockIdx.x + nt) * SKINNY_SLOT_FLOATS;
       for (int c = 0; c < SKINNY_TILE_N / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + acc.s * SKINNY_TILE_N + c * 32, v);
         tmem_ld_wait();
-        if (lane < p.M) {
-          const long long base = static_cast<long long>(lane) * p.N + n0 + c * 32;
+        if (lane < SKINNY_ROWS) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(&ctrl->xpose[lane][j * 4]) = make_uint4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        }
+        __syncwarp();
+        const int col = n0 + c * 32 + t_chunk * 4;  // N is a multiple of 8: four columns never straddle N
+#pragma unroll
+        for (int pass = 0; pass < SKINNY_ROWS / 4; ++pass) {
+          const int m = pass * 4 + t_row;
+          const float4 f = *reinterpret_cast<const float4*>(&ctrl->xpose[m][t_chunk * 4]);
           if (whole_k) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2)
-              if (n0 + c * 32 + j < p.N)  // N is even
-                *reinterpret_cast<uint32_t*>(p.out + base + j) =
-                    pack_bf16x2(__uint_as_float(v[j]) * my_rinv, __uint_as_float(v[j + 1]) * my_rinv);
+            if (m < p.M && col < p.N) {
+              const float ri = ctrl->rinv[m];
+              uint2 o;
+              o.x = pack_bf16x2(f.x * ri, f.y * ri);
+              o.y = pack_bf16x2(f.z * ri, f.w * ri);
+              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + col) = o;
+            }
           } else {
-            // 16-byte vector reductions: N is a multiple of 8, so a group of four never straddles N
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (n0 + c * 32 + j < p.N)
-                atomicAdd(reinterpret_cast<float4*>(p.scratch + base + j),
-                          make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                                      __uint_as_float(v[j + 3])));
+            // this CTA's partial tile goes to a slot of its own (CTA index + tile index is unique
+            // along the chain of K ranges)
+            __stcg(reinterpret_cast<float4*>(slot + m * SKINNY_TILE_N + c * 32 + t_chunk * 4), f);
           }
         }
+        __syncwarp();  // the next chunk overwrites the staging rows
       }
       tc_fence_before();
       __syncwarp();
@@ -288,13 +306,13 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         if (lane == 0) seen = atomicAdd(p.tile_count + nt, seg_blocks) + seg_blocks;
         seen = __shfl_sync(0xffffffffu, seen, 0);
         if (seen == nkb) {
-          // last contribution to this tile: every partial is visible; scale, store, and leave
-          // scratch and counter zero for the next launch
+          // last contribution to this tile: every partial is visible.  The contributors are the
+          // CTAs whose K ranges meet this tile, found from the same partition arithmetic; sum their
+          // slots, scale, store, and leave the counter zero for the next launch.
           __threadfence();
-          // 16-byte loads, 16 of them (8 rows x 256 columns) in flight per lane before the first
-          // store: one L2 round trip per cell would otherwise dominate the kernel's tail (the
-          // compiler cannot hoist loads over possibly-aliasing stores).  N is a multiple of 8, so a
-          // group of four columns never straddles N.
+          const long long G = gridDim.x;
+          const int c_lo = static_cast<int>(((static_cast<long long>(nt) * nkb + 1) * G - 1) / total_units);
+          const int c_hi = static_cast<int>(((static_cast<long long>(nt + 1) * nkb) * G - 1) / total_units);
           static_assert(SKINNY_TILE_N == 256 && SKINNY_ROWS == 16, "finalize covers 2 x 128 columns, 2 x 8 rows");
 #pragma unroll 1
           for (int half = 0; half < 2; ++half) {
@@ -302,25 +320,35 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
 #pragma unroll
             for (int r = 0; r < 8; ++r)
 #pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
-                v[r][j] = (m < p.M && nn < p.N)
-                              ? __ldcg(reinterpret_cast<const float4*>(p.scratch + static_cast<long long>(m) * p.N + nn))
-                              : make_float4(0.f, 0.f, 0.f, 0.f);
-              }
+              for (int j = 0; j < 2; ++j) v[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int cc = c_lo; cc <= c_hi; ++cc) {
+              if (total_units * cc / G == total_units * (cc + 1) / G) continue;  // a CTA with no units
+              const float* slot = p.partial + static_cast<size_t>(cc + nt) * SKINNY_SLOT_FLOATS;
+              // 16 independent 16-byte loads in flight per lane (8 rows x 2 column groups)
+              float4 t[8][2];
+#pragma unroll
+              for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                  t[r][j] = __ldcg(reinterpret_cast<const float4*>(slot + (half * 8 + r) * SKINNY_TILE_N + j * 128 + lane * 4));
+#pragma unroll
+              for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  v[r][j].x += t[r][j].x; v[r][j].y += t[r][j].y; v[r][j].z += t[r][j].z; v[r][j].w += t[r][j].w;
+                }
+            }
 #pragma unroll
             for (int r = 0; r < 8; ++r)
 #pragma unroll
               for (int j = 0; j < 2; ++j) {
                 const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
-                if (m < p.M && nn < p.N) {
+                if (m < p.M && nn < p.N) {  // N is a multiple of 8: a group of four columns never straddles N
                   const float ri = ctrl->rinv[m];
                   uint2 o;
                   o.x = pack_bf16x2(v[r][j].x * ri, v[r][j].y * ri);
                   o.y = pack_bf16x2(v[r][j].z * ri, v[r][j].w * ri);
                   *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + nn) = o;
-                  __stcg(reinterpret_cast<float4*>(p.scratch + static_cast<long long>(m) * p.N + nn),
-                         make_float4(0.f, 0.f, 0.f, 0.f));
                 }
               }
           }
