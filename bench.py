@@ -276,26 +276,38 @@ def run_ours(args) -> None:
         kernels.matmul_lhsT_rhs(a, b, cfg=cfg, out=out, status=status)
 
     # End-to-end step: pinned host -> device copies of both operands, the kernel, device -> host
-    # copy of C.  Two buffer sets and a second stream let the D2H of step i run while the H2D
-    # of step i+1 is in flight (PCIe is full duplex); every step still moves all of its bytes.
+    # copy of C.  Two buffer sets and one stream each for uploads, kernels and downloads let the
+    # upload of step i+1 and the download of step i-1 run while the kernel of step i does (PCIe is
+    # full duplex); every step still moves all of its bytes.
     d2h_stream = torch.cuda.Stream()
     sets = [dict(a=a, b=b, out=out),
             dict(a=torch.empty_like(a), b=torch.empty_like(b), out=torch.empty_like(out))]
     d2h_done = [None, None]
+    kernel_done = [None, None]
+    h2d_stream = torch.cuda.Stream()
     e2e_count = [0]
 
     def step_e2e():
+        # three engines in flight: the upload of step i runs on its own stream while the kernel of
+        # step i-1 runs on the main stream and the download of step i-2 on a third; two buffer sets
         i = e2e_count[0]
         e2e_count[0] += 1
         cur = sets[i % 2]
         main = torch.cuda.current_stream()
+        with torch.cuda.stream(h2d_stream):
+            if kernel_done[i % 2] is not None:
+                h2d_stream.wait_event(kernel_done[i % 2])  # the kernel that last read this set has finished
+            cur["a"].copy_(a_host, non_blocking=True)
+            cur["b"].copy_(b_host, non_blocking=True)
+            uploaded = torch.cuda.Event()
+            uploaded.record(h2d_stream)
+        main.wait_event(uploaded)
         if d2h_done[i % 2] is not None:
             main.wait_event(d2h_done[i % 2])  # this set's previous result has left the device
-        cur["a"].copy_(a_host, non_blocking=True)
-        cur["b"].copy_(b_host, non_blocking=True)
         kernels.matmul_lhsT_rhs(cur["a"], cur["b"], cfg=cfg, out=cur["out"], status=status)
         ready = torch.cuda.Event()
         ready.record(main)
+        kernel_done[i % 2] = ready
         with torch.cuda.stream(d2h_stream):
             d2h_stream.wait_event(ready)
             c_host.copy_(cur["out"], non_blocking=True)
@@ -308,6 +320,7 @@ def run_ours(args) -> None:
         ranks.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        h2d_stream.wait_stream(torch.cuda.current_stream())  # uploads start inside the timed region
         for _ in range(steps):
             step_e2e()
         torch.cuda.current_stream().wait_stream(d2h_stream)  # the last result is on the host
