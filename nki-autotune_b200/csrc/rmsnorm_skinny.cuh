@@ -53,9 +53,10 @@ struct alignas(16) SkinnyCtrl {
   uint32_t tmem_base;
   volatile int abort_flag;
   float rinv[SKINNY_ROWS];
-  // drain staging: 16 rows x 32 fp32 columns, rows padded to 144 bytes so that both the row-wise
-  // writes and the transposed reads are free of bank conflicts
-  alignas(16) float xpose[SKINNY_ROWS][36];
+  // drain staging: one whole partial tile, 16 rows x 256 fp32 columns, rows padded by 16 bytes so
+  // that the row-per-lane writes of the drain and the row-wise reads after it are free of bank
+  // conflicts
+  alignas(16) float tile_s[SKINNY_ROWS][SKINNY_TILE_N + 4];
 };
 
 struct SkinnyWait {
@@ -205,6 +206,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         if (!ok) break;
         umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[acc.s]));
         acc.advance(SKINNY_ACC_BUFS);
+
       }
     }
     __syncwarp();
@@ -259,12 +261,9 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       tc_fence_after();
       const int n0 = nt * SKINNY_TILE_N;
       const bool whole_k = (seg_blocks == nkb);  // this CTA summed the tile's whole K range
-      // Lane m holds row m of the accumulator, 32 columns per load.  Storing that way would put 16
-      // different rows in every store instruction (16-byte pieces of 16 lines), which the memory
-      // pipe takes one piece at a time; the chunk is transposed through shared memory instead so
-      // that eight lanes cover one row's 128 bytes and an instruction writes four whole lines.
-      const int t_row = lane >> 3, t_chunk = lane & 7;  // transposed view: 4 rows x 8 chunks per pass
-      float* const slot = p.partial + static_cast<size_t>(blockIdx.x + nt) * SKINNY_SLOT_FLOATS;
+      // Lane m holds row m of the accumulator.  Stores straight from that layout would put 16
+      // different rows into every instruction, so the tile first goes to shared memory (which also
+      // frees the accumulator early); everything after reads it row-wise, 512 bytes per instruction.
       for (int c = 0; c < SKINNY_TILE_N / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + acc.s * SKINNY_TILE_N + c * 32, v);
@@ -272,89 +271,95 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         if (lane < SKINNY_ROWS) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(&ctrl->xpose[lane][j * 4]) = make_uint4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            *reinterpret_cast<uint4*>(&ctrl->tile_s[lane][c * 32 + j * 4]) =
+                make_uint4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
         }
-        __syncwarp();
-        const int col = n0 + c * 32 + t_chunk * 4;  // N is a multiple of 8: four columns never straddle N
-#pragma unroll
-        for (int pass = 0; pass < SKINNY_ROWS / 4; ++pass) {
-          const int m = pass * 4 + t_row;
-          const float4 f = *reinterpret_cast<const float4*>(&ctrl->xpose[m][t_chunk * 4]);
-          if (whole_k) {
-            if (m < p.M && col < p.N) {
-              const float ri = ctrl->rinv[m];
-              uint2 o;
-              o.x = pack_bf16x2(f.x * ri, f.y * ri);
-              o.y = pack_bf16x2(f.z * ri, f.w * ri);
-              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + col) = o;
-            }
-          } else {
-            // this CTA's partial tile goes to a slot of its own (CTA index + tile index is unique
-            // along the chain of K ranges)
-            __stcg(reinterpret_cast<float4*>(slot + m * SKINNY_TILE_N + c * 32 + t_chunk * 4), f);
-          }
-        }
-        __syncwarp();  // the next chunk overwrites the staging rows
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[acc.s]));
+      static_assert(SKINNY_TILE_N == 256 && SKINNY_ROWS == 16, "row-wise passes cover 2 x 128 columns, 2 x 8 rows");
+      const long long G = gridDim.x;
+      bool last = whole_k;
       if (!whole_k) {
-        __threadfence();
-        __syncwarp();
-        int seen = 0;
-        if (lane == 0) seen = atomicAdd(p.tile_count + nt, seg_blocks) + seg_blocks;
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (seen == nkb) {
-          // last contribution to this tile: every partial is visible.  The contributors are the
-          // CTAs whose K ranges meet this tile, found from the same partition arithmetic; sum their
-          // slots, scale, store, and leave the counter zero for the next launch.
+        // Contributors publish their partial tile (slot index = CTA index + tile index, unique along
+        // the chain of K ranges) and then add their k-blocks to the tile's counter; whoever brings
+        // it to nkb sums up.  A contributor that finds all the others already counted is known to
+        // be the last without publishing anything: its own partial stays in shared memory.
+        int before = 0;
+        if (lane == 0) before = ld_acquire_gpu(p.tile_count + nt);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        last = (before + seg_blocks == nkb);
+        if (!last) {
+          float* const slot = p.partial + static_cast<size_t>(blockIdx.x + nt) * SKINNY_SLOT_FLOATS;
+#pragma unroll
+          for (int m = 0; m < SKINNY_ROWS; ++m)
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              __stcg(reinterpret_cast<float4*>(slot + m * SKINNY_TILE_N + j * 128 + lane * 4),
+                     *reinterpret_cast<const float4*>(&ctrl->tile_s[m][j * 128 + lane * 4]));
           __threadfence();
-          const long long G = gridDim.x;
-          const int c_lo = static_cast<int>(((static_cast<long long>(nt) * nkb + 1) * G - 1) / total_units);
-          const int c_hi = static_cast<int>(((static_cast<long long>(nt + 1) * nkb) * G - 1) / total_units);
-          static_assert(SKINNY_TILE_N == 256 && SKINNY_ROWS == 16, "finalize covers 2 x 128 columns, 2 x 8 rows");
+          __syncwarp();
+          int seen = 0;
+          if (lane == 0) seen = atomicAdd(p.tile_count + nt, seg_blocks) + seg_blocks;
+          seen = __shfl_sync(0xffffffffu, seen, 0);
+          last = (seen == nkb);  // the others finished in the meantime
+        }
+        if (last) __threadfence();  // the other contributors' partials are visible from here on
+      }
+      if (last) {
+        // sum of the contributors' partials in CTA order, whoever does the summing (the result does
+        // not depend on which contributor came last): this CTA's from shared memory, the others'
+        // from their slots, found from the same partition arithmetic; scale, store, and leave the
+        // counter zero for the next launch
+        int c_lo = static_cast<int>(blockIdx.x), c_hi = static_cast<int>(blockIdx.x);
+        if (!whole_k) {
+          c_lo = static_cast<int>(((static_cast<long long>(nt) * nkb + 1) * G - 1) / total_units);
+          c_hi = static_cast<int>(((static_cast<long long>(nt + 1) * nkb) * G - 1) / total_units);
+        }
 #pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            float4 v[8][2];
+        for (int half = 0; half < 2; ++half) {
+          float4 v[8][2];
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) v[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int cc = c_lo; cc <= c_hi; ++cc) {
+            if (total_units * cc / G == total_units * (cc + 1) / G) continue;     // a CTA with no units
+            const bool mine = (cc == static_cast<int>(blockIdx.x));
+            const float* other = p.partial + static_cast<size_t>(cc + nt) * SKINNY_SLOT_FLOATS;
+            // 16 independent 16-byte loads in flight per lane (8 rows x 2 column groups)
+            float4 t[8][2];
 #pragma unroll
             for (int r = 0; r < 8; ++r)
 #pragma unroll
-              for (int j = 0; j < 2; ++j) v[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int cc = c_lo; cc <= c_hi; ++cc) {
-              if (total_units * cc / G == total_units * (cc + 1) / G) continue;  // a CTA with no units
-              const float* slot = p.partial + static_cast<size_t>(cc + nt) * SKINNY_SLOT_FLOATS;
-              // 16 independent 16-byte loads in flight per lane (8 rows x 2 column groups)
-              float4 t[8][2];
-#pragma unroll
-              for (int r = 0; r < 8; ++r)
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
-                  t[r][j] = __ldcg(reinterpret_cast<const float4*>(slot + (half * 8 + r) * SKINNY_TILE_N + j * 128 + lane * 4));
-#pragma unroll
-              for (int r = 0; r < 8; ++r)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                  v[r][j].x += t[r][j].x; v[r][j].y += t[r][j].y; v[r][j].z += t[r][j].z; v[r][j].w += t[r][j].w;
-                }
-            }
+              for (int j = 0; j < 2; ++j)
+                t[r][j] = mine ? *reinterpret_cast<const float4*>(&ctrl->tile_s[half * 8 + r][j * 128 + lane * 4])
+                               : __ldcg(reinterpret_cast<const float4*>(other + (half * 8 + r) * SKINNY_TILE_N + j * 128 + lane * 4));
 #pragma unroll
             for (int r = 0; r < 8; ++r)
 #pragma unroll
               for (int j = 0; j < 2; ++j) {
-                const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
-                if (m < p.M && nn < p.N) {  // N is a multiple of 8: a group of four columns never straddles N
-                  const float ri = ctrl->rinv[m];
-                  uint2 o;
-                  o.x = pack_bf16x2(v[r][j].x * ri, v[r][j].y * ri);
-                  o.y = pack_bf16x2(v[r][j].z * ri, v[r][j].w * ri);
-                  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + nn) = o;
-                }
+                v[r][j].x += t[r][j].x; v[r][j].y += t[r][j].y; v[r][j].z += t[r][j].z; v[r][j].w += t[r][j].w;
               }
           }
-          if (lane == 0) p.tile_count[nt] = 0;
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
+              if (m < p.M && nn < p.N) {  // N is a multiple of 8: a group of four columns never straddles N
+                const float ri = ctrl->rinv[m];
+                uint2 o;
+                o.x = pack_bf16x2(v[r][j].x * ri, v[r][j].y * ri);
+                o.y = pack_bf16x2(v[r][j].z * ri, v[r][j].w * ri);
+                *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + nn) = o;
+              }
+            }
         }
+        if (!whole_k && lane == 0) p.tile_count[nt] = 0;
       }
+      __syncwarp();  // the next segment's drain overwrites the staging tile
       u = seg_end;
       acc.advance(SKINNY_ACC_BUFS);
     }
