@@ -286,6 +286,10 @@ def run_ours(args) -> None:
     kernel_done = [None, None]
     h2d_stream = torch.cuda.Stream()
     e2e_count = [0]
+    # With several ranks the replicated rhs crosses PCIe once per step (rank 0 uploads it) and
+    # reaches the other GPUs over NVLink (NCCL broadcast into each rank's own buffer); every
+    # rank still uploads its own lhsT block and downloads its own block of C.
+    nccl = ranks.nccl_group() if ranks.world > 1 else None
 
     def step_e2e():
         # three engines in flight: the upload of step i runs on its own stream while the kernel of
@@ -298,7 +302,10 @@ def run_ours(args) -> None:
             if kernel_done[i % 2] is not None:
                 h2d_stream.wait_event(kernel_done[i % 2])  # the kernel that last read this set has finished
             cur["a"].copy_(a_host, non_blocking=True)
-            cur["b"].copy_(b_host, non_blocking=True)
+            if nccl is None or ranks.rank == 0:
+                cur["b"].copy_(b_host, non_blocking=True)
+            if nccl is not None:
+                ranks.dist.broadcast(cur["b"], src=0, group=nccl)
             uploaded = torch.cuda.Event()
             uploaded.record(h2d_stream)
         main.wait_event(uploaded)
@@ -380,11 +387,20 @@ def run_ours(args) -> None:
             "ms_per_step": round(ms_e2e, 4),
             "h2d_bytes_per_step": int(a_host.numel() * 2 + b_host.numel() * 2),
             "d2h_bytes_per_step": int(c_host.numel() * 2),
+            **({} if ranks.world == 1 else {
+                "note": "bytes of rank 0; the other ranks upload lhsT only (half) and receive rhs by NCCL broadcast over NVLink",
+                "h2d_bytes_per_step_all_ranks": int(ranks.world * a_host.numel() * 2 + b_host.numel() * 2),
+                "nvlink_broadcast_bytes_per_step": int(b_host.numel() * 2)}),
         },
         "gpu_launches": args.steps,
         "clocks": clocks,
     }
 
+    if ranks.world > 1:
+        # every rank multiplied the same operands (its rhs came over NVLink): the downloaded results must agree
+        sums = ranks.gather(float(c_host[::64].float().sum()))
+        if ranks.rank == 0:
+            line["e2e"]["results_agree_across_ranks"] = all(x == sums[0] for x in sums)
     if ranks.rank == 0 and ranks.world == 1:
         # parity of what was just timed, and the CPU baseline on a bounded sample (2048 of 8192 rows)
         sample = 2048
