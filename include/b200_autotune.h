@@ -57,7 +57,12 @@ typedef struct b200_cfg {
                      launch first writes x*gamma and rinv to scratch, then runs the plain main
                      loop; needs b200_workspace_bytes of scratch), 0 = prologue when a large
                      enough workspace is passed, else inline                                */
-  int reserved[7];
+  int reserved[7]; /* zero in normal use.  Measurement and test hooks: [0] 1 = the TMA producer issues
+                     nothing (makes the consumers' bounded waits run out), 2 = operands loaded once
+                     per stage slot, 3 = UMMAs not issued, 4 = transform work skipped (inline fused
+                     kernel); [1] limit of a device-side wait in microseconds (default 1 s);
+                     [2] 1 = GEMM kernel stores its longest CTA lifetime in dev_status[6] (SM cycles)
+                     and [7] (nanoseconds)                                                      */
 } b200_cfg;
 
 /* Number of ints in a dev_status block (device memory, caller-owned, zeroed by caller).
