@@ -15,7 +15,7 @@ from pathlib import Path
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "nki-autotune_b200"))
 
 from autotune.runner.api import profile  # noqa: E402
-from autotune.runner.candidate import Candidate, enumerate_grid, jobs_from_candidates  # noqa: E402
+from autotune.runner.candidate import Candidate, enumerate_grid, extended_grid, jobs_from_candidates  # noqa: E402
 
 
 def main() -> None:
@@ -36,6 +36,10 @@ def main() -> None:
             for c in enumerate_grid("rmsnorm_matmul", stages=(2, 3, 4, 6), scalars={"eps": eps}):
                 cfg = dict(c.config, norm_mode=mode)
                 cands.append(Candidate("rmsnorm_matmul", cfg, dict(c.scalars)))
+        # the prologue variant runs the plain GEMM main loop, so the large pair tiles apply to it too
+        for c in extended_grid("rmsnorm_matmul", scalars={"eps": eps})[64:]:
+            if c.config["tile_m"] == 512:
+                cands.append(Candidate("rmsnorm_matmul", dict(c.config, norm_mode=2), dict(c.scalars)))
     specs = {"x": ((m, k), "bfloat16"), "gamma": ((k,), "bfloat16", {"kind": "uniform", "low": 0.5, "high": 1.5}),
              "weight": ((k, n), "bfloat16", {"kind": "normal", "scale": k ** -0.5})}
     cache_dir = os.path.join(args.cache, "tune_rmsnorm_matmul" + ("_skinny" if args.skinny else ""))

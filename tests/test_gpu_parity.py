@@ -191,6 +191,14 @@ def test_rmsnorm_golden_cases(K, golden, key, seed, m, k, n, eps, c):
     assert O.max_abs_rel_err(got, expect) <= TOL_BF16
 
 
+@pytest.mark.parametrize("m,k,n", [(1000, 512, 1016), (2048, 2048, 2048), (520, 64, 264)])
+@pytest.mark.parametrize("c", [cfg(512, 256, 64, 4, cm=2, nm=2), cfg(512, 128, 128, 2, cm=2, nm=2), cfg(256, 512, 64, 4, cm=2, nm=2)],
+                         ids=["512x256", "512x128-k128", "256x512"])
+def test_rmsnorm_prologue_variant_with_large_pair_tiles(K, m, k, n, c):
+    got, expect = _rms_case(K, 13, m, k, n, 1e-6, c)
+    assert O.max_abs_rel_err(got, expect) <= TOL_BF16
+
+
 @pytest.mark.parametrize("nm", [1, 2], ids=["inline", "prologue"])
 @pytest.mark.parametrize("m,k,n", [(256, 512, 384), (1000, 512, 1016), (2048, 2048, 2048), (136, 64, 72)])
 @pytest.mark.parametrize("tiles", [(128, 128, 64, 3, 1), (128, 256, 128, 2, 1), (256, 256, 64, 4, 2), (256, 256, 128, 3, 2),
