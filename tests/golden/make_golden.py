@@ -18,6 +18,7 @@ reference's recipe (one ``default_rng(seed)``, tensors drawn in order).
 from __future__ import annotations
 
 import argparse
+import os
 import importlib.util
 import sys
 from pathlib import Path
@@ -56,7 +57,8 @@ def bf16_round(a: np.ndarray) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("NKI_AUTOTUNE_REFERENCE"), required="NKI_AUTOTUNE_REFERENCE" not in os.environ,
+                    help="checkout of awslabs/nki-autotune (or set NKI_AUTOTUNE_REFERENCE)")
     args = ap.parse_args()
     ref = Path(args.reference)
     sys.path.insert(0, str(HERE))
