@@ -86,6 +86,12 @@ int b200_device_count(int* count);
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
                    long* smem_bytes, int* tmem_cols);
 
+/* The candidate the library uses when an entry point is called with cfg == NULL, for this family
+ * and shape (the fused family: norm_mode 0 and the tile of the variant that runs without scratch).
+ * The reference has no counterpart: its hand kernels carry fixed tile constants
+ * (kernel_library/matmul/lhsT_rhs/kernel_hand_90.92mfu.py:103-105). */
+int b200_default_cfg(const char* family, long M, long N, long K, b200_cfg* cfg);
+
 /* Bytes of device scratch the candidate can use (0 when it needs none).  The scratch must be
  * zero-filled once before first use; the kernels leave it reusable for the next launch.  After
  * a launch that ended with B200_ERR_DEVICE_WAIT its contents are undefined: zero it again.

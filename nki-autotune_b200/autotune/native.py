@@ -83,6 +83,7 @@ SIGNATURES = {
         C.c_int,
         [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long, C.POINTER(C.c_long), C.POINTER(C.c_int)],
     ),
+    "b200_default_cfg": (C.c_int, [C.c_char_p, C.c_long, C.c_long, C.c_long, C.POINTER(Cfg)]),
     "b200_workspace_bytes": (C.c_size_t, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long]),
     "b200_matmul_lhsT_rhs": (
         C.c_int,
@@ -148,6 +149,13 @@ def last_error() -> str:
 def check(status: int) -> None:
     if status != OK:
         raise NativeError(status, last_error())
+
+
+def default_cfg(family: str, M: int, N: int, K: int) -> dict:
+    """The candidate the library picks for this family and shape when no cfg is given."""
+    c = Cfg()
+    check(load().b200_default_cfg(family.encode(), M, N, K, C.byref(c)))
+    return {name: int(getattr(c, name)) for name in CFG_FIELDS}
 
 
 def cfg_check(family: str, cfg: dict | None, M: int = 0, N: int = 0, K: int = 0) -> tuple[int, str, int, int]:

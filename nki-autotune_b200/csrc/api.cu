@@ -63,19 +63,42 @@ struct Plan {
 };
 
 // Best configurations measured on B200 for the benchmark shapes.
-static b200_cfg default_cfg(Family fam, long M) {
+// Default candidate when the caller passes no b200_cfg.  For the plain GEMM main loop the choice
+// is the candidate with the smallest estimated time: rounds of the persistent schedule (tiles over
+// the CTA groups of a 148-SM part) x tile area per SM / relative throughput of that tile shape
+// as measured at 8192^3.  Large problems get the 512x256 pair tile; short ones a smaller tile that
+// fills the machine.
+static b200_cfg default_cfg(Family fam, long M, long N) {
   b200_cfg c;
   memset(&c, 0, sizeof(c));
   c.cluster_n = 1;
   if (fam == FAM_RMSNORM && M > 0 && M <= 16) {  // weight-streaming kernel
     c.tile_m = 16; c.tile_n = 256; c.tile_k = 128; c.stages = 3; c.cluster_m = 1;
-  } else if (fam == FAM_RMSNORM) {
-    c.tile_m = 128; c.tile_n = 256; c.tile_k = 128; c.stages = 2; c.cluster_m = 1;
-  } else if (M >= 2048) {  // enough rows for 512-row pair tiles: least operand traffic per flop
-    c.tile_m = 512; c.tile_n = 256; c.tile_k = 64; c.stages = 4; c.cluster_m = 2;
-  } else {
-    c.tile_m = 256; c.tile_n = 256; c.tile_k = 128; c.stages = 3; c.cluster_m = 2;
+    return c;
   }
+  if (fam == FAM_RMSNORM) {  // inline norm
+    c.tile_m = 128; c.tile_n = 256; c.tile_k = 128; c.stages = 2; c.cluster_m = 1;
+    return c;
+  }
+  struct Option { int tile_m, tile_n, tile_k, stages, cluster_m; double rate; };
+  static const Option kOptions[] = {
+      {512, 256, 64, 4, 2, 1.00},
+      {256, 256, 128, 3, 2, 0.96},
+      {128, 256, 128, 2, 1, 0.76},
+  };
+  const Option* best = &kOptions[1];
+  if (M > 0 && N > 0) {
+    double best_cost = 0.0;
+    for (const Option& o : kOptions) {
+      const long tiles = ((M + o.tile_m - 1) / o.tile_m) * ((N + o.tile_n - 1) / o.tile_n);
+      const long groups = 148 / o.cluster_m;
+      const long rounds = (tiles + groups - 1) / groups;
+      const double cost = static_cast<double>(rounds) * o.tile_m * o.tile_n / o.cluster_m / o.rate;  // per-SM work
+      if (best_cost == 0.0 || cost < best_cost) { best_cost = cost; best = &o; }
+    }
+  }
+  c.tile_m = best->tile_m; c.tile_n = best->tile_n; c.tile_k = best->tile_k; c.stages = best->stages;
+  c.cluster_m = best->cluster_m;
   return c;
 }
 
@@ -89,7 +112,7 @@ static int next_pow2_cols(int cols) {
 static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K, Plan* plan) {
   if (fam == FAM_UNKNOWN)
     return set_error(B200_ERR_BAD_ARG, "unknown kernel family (expected matmul_lhsT_rhs, matmul_lhs_rhs or rmsnorm_matmul)");
-  b200_cfg cfg = cfg_in ? *cfg_in : default_cfg(fam, M);
+  b200_cfg cfg = cfg_in ? *cfg_in : default_cfg(fam, M, N);
   if (fam == FAM_RMSNORM && M > 0 && M <= SKINNY_ROWS) {
     // skinny activations: the weight-streaming kernel; only tile_k and stages apply
     Plan sp;
@@ -416,7 +439,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
       return set_error(B200_ERR_WORKSPACE, "rmsnorm_matmul with norm_mode 2 needs %zu bytes of device workspace (got %zu)",
                        prologue_workspace_bytes(la.M, la.K), la.workspace ? la.workspace_bytes : static_cast<size_t>(0));
     if (mode == 2 || (mode == 0 && have_ws)) {
-      eff = cfg ? *cfg : default_cfg(FAM_LHST, la.M);
+      eff = cfg ? *cfg : default_cfg(FAM_LHST, la.M, la.N);
       eff.norm_mode = 2;
       cfg = &eff;
     } else if (cfg != nullptr) {
@@ -652,6 +675,16 @@ extern "C" int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, l
   if (smem_bytes) *smem_bytes = plan.smem_bytes;
   if (tmem_cols) *tmem_cols = plan.tmem_cols;
   return rc;
+}
+
+extern "C" int b200_default_cfg(const char* family, long M, long N, long K, b200_cfg* cfg) {
+  (void)K;
+  if (!cfg) return set_error(B200_ERR_BAD_ARG, "default_cfg: NULL pointer");
+  Family fam = parse_family(family);
+  if (fam == FAM_UNKNOWN)
+    return set_error(B200_ERR_BAD_ARG, "unknown kernel family (expected matmul_lhsT_rhs, matmul_lhs_rhs or rmsnorm_matmul)");
+  *cfg = default_cfg(fam == FAM_LHS ? FAM_LHST : fam, M, N);
+  return B200_OK;
 }
 
 extern "C" size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K) {

@@ -144,6 +144,27 @@ def test_cfg_check_budgets(native_lib):
     print("accepted of the 64-point grid:", accepted, "of the 24 large-tile points:", big.count(native.OK))
 
 
+def test_default_candidate_follows_the_problem_size(native_lib):
+    """No cfg: large problems get the 512x256 pair tile, short ones a tile that still fills the
+    machine; the 16-row fused shape gets the weight-streaming kernel's stage shape."""
+    from autotune import native
+
+    def tile(fam, m, n, k):
+        d = native.default_cfg(fam, m, n, k)
+        assert native.cfg_check(fam, d, m, n, k)[0] == native.OK
+        return d["tile_m"], d["tile_n"], d["tile_k"], d["stages"], d["cluster_m"]
+
+    assert tile("matmul_lhsT_rhs", 8192, 8192, 8192) == (512, 256, 64, 4, 2)
+    assert tile("matmul_lhsT_rhs", 131072, 4096, 4096) == (512, 256, 64, 4, 2)
+    assert tile("matmul_lhs_rhs", 4096, 11008, 4096) == (512, 256, 64, 4, 2)
+    assert tile("matmul_lhsT_rhs", 256, 4096, 4096) == (256, 256, 128, 3, 2)
+    assert tile("matmul_lhsT_rhs", 512, 512, 512) == (256, 256, 128, 3, 2)
+    assert tile("rmsnorm_matmul", 16, 28672, 8192)[:1] == (16,)
+    assert tile("rmsnorm_matmul", 4096, 11008, 4096) == (128, 256, 128, 2, 1)      # inline variant (no scratch)
+    with pytest.raises(native.NativeError):
+        native.default_cfg("nope", 1, 1, 1)
+
+
 def test_cfg_check_families_and_scratch_sizes(native_lib):
     import ctypes as C
 
