@@ -31,6 +31,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=None, help="shard the candidates over this many GPUs")
     ap.add_argument("--retime-top", type=int, default=5,
                     help="after a multi-GPU sweep, time the fastest N candidates again on one GPU")
+    ap.add_argument("--split-k", default="0", help="comma-separated split-K factors to sweep as a further dimension, e.g. 0,2,4,8")
     ap.add_argument("--extended", action="store_true", help="add the 24 large-tile points (512-row / 512-column tiles)")
     args = ap.parse_args()
 
@@ -40,7 +41,8 @@ def main() -> None:
     cache_dir = os.path.join(args.cache, "tune_matmul_lhsT_rhs")
     shutil.rmtree(cache_dir, ignore_errors=True)
 
-    grid = extended_grid("matmul_lhsT_rhs") if args.extended else enumerate_grid("matmul_lhsT_rhs")
+    splits = tuple(int(v) for v in args.split_k.split(","))
+    grid = extended_grid("matmul_lhsT_rhs") if args.extended else enumerate_grid("matmul_lhsT_rhs", split_k=splits)
     jobs = jobs_from_candidates(grid, (n, n), specs)
     print(f"[tune] profiling {len(jobs)} candidates at {n}^3 ...\n")
     output = profile(jobs, cache_dir=cache_dir, seed=SEED, neuron_platform_target="b200",

@@ -51,7 +51,10 @@ typedef struct b200_cfg {
   int cluster_m;  /* 1, or 2 = a CTA pair along M (tile_m 256 or 512: 2-SM UMMAs)           */
   int cluster_n;  /* 1 (reserved)                                                          */
   int swizzle;    /* tile rasterisation group width along M (1,2,4,8,16); 0 = default      */
-  int split_k;    /* reserved (the skinny kernel balances K ranges itself); 0               */
+  int split_k;    /* plain GEMM families: 2..16 = every tile's K range is dealt to that many work
+                     units (fewer if K has fewer k-blocks), their fp32 partial tiles go to scratch
+                     (b200_workspace_bytes) and a second kernel sums them in order; for problems
+                     with fewer tiles than SMs.  0 or 1 = none                                 */
   int norm_mode;  /* rmsnorm_matmul, M > 16: where the norm is applied.  1 = inline (x tiles are
                      scaled on their way through tensor memory, no scratch), 2 = prologue (the
                      launch first writes x*gamma and rinv to scratch, then runs the plain main

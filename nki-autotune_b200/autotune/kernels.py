@@ -65,7 +65,8 @@ def workspace_for(family: str, M: int, N: int, K: int, device, cfg: dict | None 
         return None
     dev = torch.device(device)
     index = dev.index if dev.index is not None else torch.cuda.current_device()
-    key = (index, "skinny" if M <= 16 else "prologue", int(need))
+    kind = "split_k" if family != "rmsnorm_matmul" else ("skinny" if M <= 16 else "prologue")
+    key = (index, kind, int(need))
     buf = _WORKSPACES.get(key)
     if buf is None:
         buf = torch.zeros(int(need), dtype=torch.uint8, device=dev)
@@ -119,10 +120,12 @@ def matmul_lhsT_rhs(
     if lhs_T.dtype != torch.bfloat16:
         raise NativeError(native.ERR_BAD_ARG, f"unsupported dtype {lhs_T.dtype}")
     c = Cfg.from_dict(cfg)
+    ws = workspace_for("matmul_lhsT_rhs", M, N, K, lhs_T.device, cfg)  # split-K candidates only
     native.check(
         lib.b200_matmul_lhsT_rhs(
             lhs_T.data_ptr(), rhs.data_ptr(), out.data_ptr(), M, N, K, _ld(lhs_T), _ld(rhs), _ld(out),
-            C.byref(c) if c is not None else None, None, 0,
+            C.byref(c) if c is not None else None,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
             status.data_ptr() if status is not None else None, _stream_ptr(),
         )
     )
@@ -149,10 +152,12 @@ def matmul_lhs_rhs(
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=lhs.device)
     c = Cfg.from_dict(cfg)
+    ws = workspace_for("matmul_lhs_rhs", M, N, K, lhs.device, cfg)  # split-K candidates only
     native.check(
         lib.b200_matmul_lhs_rhs(
             lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(), M, N, K, _ld(lhs), _ld(rhs), _ld(out),
-            C.byref(c) if c is not None else None, None, 0,
+            C.byref(c) if c is not None else None,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
             status.data_ptr() if status is not None else None, _stream_ptr(),
         )
     )

@@ -84,18 +84,21 @@ def enumerate_grid(
     stages=(3, 4, 5, 6),
     cluster_m=(1, 2),
     swizzle=(0,),
+    split_k=(0,),
     scalars: dict | None = None,
 ) -> list[Candidate]:
     """Cartesian grid of candidates in a fixed, documented order.
 
     The default is the 64-point sweep: tile M in {128,256} x tile N in {128,256} x tile K in
     {64,128} x stages 3..6 x cluster {1x1, 2x1}.  Nothing is filtered: points that do not fit
-    shared or tensor memory are reported as failures by the validation step.
+    shared or tensor memory are reported as failures by the validation step.  ``split_k`` adds
+    the split of every tile's K range as a further dimension (plain GEMM families; worth
+    sweeping when the problem has fewer tiles than SMs).
     """
     out = []
-    for tm, tn, tk, st, cm, sw in itertools.product(tile_m, tile_n, tile_k, stages, cluster_m, swizzle):
+    for tm, tn, tk, st, cm, sw, sk in itertools.product(tile_m, tile_n, tile_k, stages, cluster_m, swizzle, split_k):
         cfg = {"tile_m": tm, "tile_n": tn, "tile_k": tk, "stages": st, "cluster_m": cm, "cluster_n": 1,
-               "swizzle": sw, "split_k": 0}
+               "swizzle": sw, "split_k": sk}
         out.append(Candidate(family=family, config=cfg, scalars=dict(scalars or {})))
     return out
 

@@ -59,10 +59,11 @@ struct Plan {
   int skinny;           // fused kernel, M <= 16: the weight-streaming kernel
   int prologue;         // fused kernel, M > 16: prologue variant of the plain GEMM (needs scratch)
   int a_kmajor;         // matmul_lhs_rhs: A is [M,K] with K contiguous
+  int split_k;          // plain GEMM: parts of the K range (1 = none); parts > 1 need scratch
+  int kb_per_part;
   long smem_bytes;
 };
 
-// Best configurations measured on B200 for the benchmark shapes.
 // Default candidate when the caller passes no b200_cfg.  For the plain GEMM main loop the choice
 // is the candidate with the smallest estimated time: rounds of the persistent schedule (tiles over
 // the CTA groups of a 148-SM part) x tile area per SM / relative throughput of that tile shape
@@ -174,6 +175,23 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     return set_error(B200_ERR_UNSUPPORTED, "stages=%d: need 1..%d", cfg.stages, MAX_STAGES);
   if (cfg.swizzle < 0 || cfg.swizzle > 64)
     return set_error(B200_ERR_UNSUPPORTED, "swizzle=%d: need 0..64", cfg.swizzle);
+  // split-K (plain GEMM families): every tile's k-blocks are dealt to split_k work units whose
+  // fp32 partial tiles a second kernel sums; parts are sized so that none is empty
+  p.split_k = 1;
+  p.kb_per_part = 0;
+  if (cfg.split_k < 0 || cfg.split_k > 16)
+    return set_error(B200_ERR_UNSUPPORTED, "split_k=%d: need 0..16", cfg.split_k);
+  if (cfg.split_k > 1) {
+    if (fam != FAM_LHST || prologue)
+      return set_error(B200_ERR_UNSUPPORTED, "split_k=%d: only the plain GEMM families can split K", cfg.split_k);
+    if (K > 0) {
+      const int nkb = static_cast<int>((K + cfg.tile_k - 1) / cfg.tile_k);
+      p.kb_per_part = (nkb + cfg.split_k - 1) / cfg.split_k;
+      p.split_k = (nkb + p.kb_per_part - 1) / p.kb_per_part;
+    } else {
+      p.split_k = cfg.split_k;
+    }
+  }
   p.group_m = cfg.swizzle > 0 ? cfg.swizzle : (cfg.tile_m == 512 ? 4 : (p.cta_group == 2 || p.m_sub == 2 ? 8 : 16));
 
   const int acc_cols = p.m_sub * p.tile_n;
@@ -276,6 +294,55 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long rows, long col
   return B200_OK;
 }
 
+// 2-D fp32 tensor [rows, cols] (row pitch ld floats), boxes of 32 columns x box_rows rows with the
+// 128-byte swizzle: the split-K partial arrays the epilogue stores into.
+static int make_tmap_f32(CUtensorMap* tm, const void* base, long rows, long cols, long ld, int box_rows,
+                         const char* what) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return set_error(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || ld % 4 != 0 || ld < cols)
+    return set_error(B200_ERR_BAD_ARG, "%s: base must be 16-byte aligned and the row pitch a multiple of 4 floats", what);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4u};
+  cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(B200_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, (int)r);
+  return B200_OK;
+}
+
+// split-K: out[m, n] = bf16(sum over parts of partial[part][m][n]), parts added in order
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, int parts, size_t part_stride, __nv_bfloat16* __restrict__ out,
+                     long ld_out, int M, int N) {
+  const long groups_per_row = N / 8;  // N is a multiple of 8
+  const long total = static_cast<long>(M) * groups_per_row;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long m = i / groups_per_row;
+    const long n = (i - m * groups_per_row) * 8;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    for (int p = 0; p < parts; ++p) {
+      const float4* src = reinterpret_cast<const float4*>(partial + p * part_stride + m * N + n);
+      const float4 x = __ldcg(src), y = __ldcg(src + 1);
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
+    o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
+    *reinterpret_cast<uint4*>(out + m * ld_out + n) = o;
+  }
+}
+
+static size_t splitk_workspace_bytes(const Plan& plan, long M, long N) {
+  if (plan.split_k <= 1) return 0;
+  const long m_pad = (M + plan.tile_m - 1) / plan.tile_m * plan.tile_m;
+  return static_cast<size_t>(plan.split_k) * m_pad * N * sizeof(float);
+}
+
 // ---------------------------------------------------------------------------- launch
 typedef void (*GemmKernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
 typedef void (*RmsKernelFn)(const CUtensorMap, const CUtensorMap, const RmsParams);
@@ -367,6 +434,8 @@ struct Prepared {
   RmsKernelFn rms_fn;   // fused kernel (fam == FAM_RMSNORM)
   CUtensorMap tm_a, tm_b, tm_out;
   GemmParams gp;
+  const float* sk_partial;   // split-K: partial arrays in the scratch, one per part
+  size_t sk_part_stride;     // floats between parts
   RmsParams rp;
   SkinnyParams sp;
   bool fused;
@@ -477,8 +546,24 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (rc) return rc;
   rc = make_tmap_bf16(&pr->tm_b, la.b, la.K, la.N, la.ld_b, 64, plan.tile_k, la.fam == FAM_RMSNORM ? "w" : "rhs");
   if (rc) return rc;
-  // the epilogue stores 32-row x 64-column boxes; rows and columns past M and N are clipped
-  rc = make_tmap_bf16(&pr->tm_out, la.out, la.M, la.N, la.ld_out, 64, 32, "out");
+  pr->sk_partial = nullptr;
+  pr->sk_part_stride = 0;
+  if (plan.split_k > 1) {
+    // the epilogue stores fp32 boxes into [part][padded rows][N] arrays in the scratch; ragged
+    // tiles spill into a part's own padding rows and columns past N are clipped
+    const size_t need = splitk_workspace_bytes(plan, la.M, la.N);
+    if (la.workspace == nullptr || la.workspace_bytes < need)
+      return set_error(B200_ERR_WORKSPACE, "split_k=%d needs %zu bytes of device workspace (got %zu)", plan.split_k,
+                       need, la.workspace ? la.workspace_bytes : static_cast<size_t>(0));
+    const long m_pad = (la.M + plan.tile_m - 1) / plan.tile_m * plan.tile_m;
+    rc = make_tmap_f32(&pr->tm_out, la.workspace, static_cast<long>(plan.split_k) * m_pad, la.N, la.N, 32,
+                       "split-K partials (workspace)");
+    pr->sk_partial = static_cast<const float*>(la.workspace);
+    pr->sk_part_stride = static_cast<size_t>(m_pad) * la.N;
+  } else {
+    // the epilogue stores 32-row x 64-column boxes; rows and columns past M and N are clipped
+    rc = make_tmap_bf16(&pr->tm_out, la.out, la.M, la.N, la.ld_out, 64, 32, "out");
+  }
   if (rc) return rc;
 
   GemmParams& gp = pr->gp;
@@ -494,6 +579,9 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   gp.num_n_tiles = static_cast<int>((la.N + plan.tile_n - 1) / plan.tile_n);
   gp.num_k_blocks = static_cast<int>((la.K + plan.tile_k - 1) / plan.tile_k);
   gp.group_m = plan.group_m;
+  gp.split_k = plan.split_k;
+  gp.kb_per_part = plan.split_k > 1 ? plan.kb_per_part : gp.num_k_blocks;
+  gp.part_rows = static_cast<int>((la.M + plan.tile_m - 1) / plan.tile_m * plan.tile_m);
   gp.acc_bufs = plan.acc_bufs;
   gp.tmem_cols = plan.tmem_cols;
   gp.ld_out = la.ld_out;
@@ -555,7 +643,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
                   "cudaFuncSetAttribute(max dynamic shared memory)");
   if (rc) return rc;
 
-  const long total_tiles = static_cast<long>(gp.num_m_tiles) * gp.num_n_tiles;
+  const long total_tiles = static_cast<long>(gp.num_m_tiles) * gp.num_n_tiles * plan.split_k;  // work units
   long groups = di.sm_count / plan.cluster;  // CTA groups (clusters) that fit the machine
   if (plan.cluster > 1) {
     cudaLaunchConfig_t qc;
@@ -644,7 +732,13 @@ static int launch(const Prepared& pr, cudaStream_t stream) {
     return check_cuda(cudaLaunchKernelEx(&lc, rmsnorm_skinny_kernel, pr.tm_b, pr.sp), "skinny RMSNorm GEMM launch");
   if (pr.fused)
     return check_cuda(cudaLaunchKernelEx(&lc, pr.rms_fn, pr.tm_a, pr.tm_b, pr.rp), "fused RMSNorm GEMM launch");
-  return check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.tm_out, pr.gp), "tcgen05 GEMM launch");
+  int rc = check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.tm_out, pr.gp), "tcgen05 GEMM launch");
+  if (rc || pr.plan.split_k <= 1) return rc;
+  const long groups = static_cast<long>(pr.gp.M) * (pr.gp.N / 8);
+  const unsigned blocks = static_cast<unsigned>(groups / 256 + 1 < 148L * 8 ? groups / 256 + 1 : 148L * 8);
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(pr.sk_partial, pr.plan.split_k, pr.sk_part_stride, pr.gp.out,
+                                                   pr.gp.ld_out, pr.gp.M, pr.gp.N);
+  return check_cuda(cudaGetLastError(), "split-K reduction launch");
 }
 
 }  // namespace b200
@@ -688,6 +782,12 @@ extern "C" int b200_default_cfg(const char* family, long M, long N, long K, b200
 }
 
 extern "C" size_t b200_workspace_bytes(const char* family, const b200_cfg* cfg, long M, long N, long K) {
+  if (parse_family(family) != FAM_RMSNORM && cfg != nullptr && cfg->split_k > 1 && M > 0 && N > 0 && K > 0) {
+    Plan plan;
+    memset(&plan, 0, sizeof(plan));
+    if (make_plan(parse_family(family), cfg, M, N, K, &plan) != B200_OK) return 0;
+    return splitk_workspace_bytes(plan, M, N);
+  }
   if (parse_family(family) != FAM_RMSNORM || M <= 0) return 0;
   if (M <= SKINNY_ROWS) return N > 0 ? skinny_workspace_bytes(N) : 0;
   if (cfg != nullptr && cfg->norm_mode == 1) return 0;  // inline norm needs no scratch

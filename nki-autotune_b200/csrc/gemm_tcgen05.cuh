@@ -50,6 +50,9 @@ struct GemmParams {
   __nv_bfloat16* out;
   int* status;       // B200_DEV_STATUS_INTS ints or nullptr
   long long timeout_cycles;
+  int split_k;       // parts the K range of every tile is split into (1 = none); parts are separate work units
+  int kb_per_part;   // k-blocks per part
+  int part_rows;     // split-K: rows of one part's fp32 partial array (num_m_tiles x tile rows)
   int debug_mode;    // 0, or one of the DEBUG_* hooks
   int record_clocks; // measurement aid: status[6]/[7] = longest CTA lifetime in SM cycles / nanoseconds
   // NORM variant only (fused RMSNorm with an in-kernel prologue):
@@ -177,7 +180,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int acc_cols = M_SUB * tile_n;
   const int acc_bufs = p.acc_bufs;
   const int num_k_blocks = p.num_k_blocks;
-  const int total_tiles = p.num_m_tiles * p.num_n_tiles;
+  // work units: (tile, part of its K range); without split-K a unit is a tile
+  const int split_k = p.split_k;
+  const int total_tiles = p.num_m_tiles * p.num_n_tiles * split_k;
   const int first_tile = static_cast<int>(blockIdx.x) / CTA_GROUP;
   const int tile_stride = static_cast<int>(gridDim.x) / CTA_GROUP;
 
@@ -302,12 +307,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       Ring ring;
       bool ok = true;
       const int b_chunks = nc / 64, sub_chunks = nc_sub / 64, sub_jump = umma_n - nc_sub;
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
+      for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride) {
+        const int tile = unit / split_k, part = unit - tile * split_k;
+        const int kb0 = part * p.kb_per_part, kb1 = min(kb0 + p.kb_per_part, num_k_blocks);
         int mt, nt;
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
         const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc_sub;  // first UMMA's share; next at + umma_n
-        for (int kb = 0; kb < num_k_blocks; ++kb, ++it, ring.advance(stages)) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it, ring.advance(stages)) {
           const uint32_t s = ring.s;
           const uint32_t ph = ring.ph;
           ok = bounded_wait<false>(wctx, smem_u32(&ctrl->empty[s]), ph ^ 1u, 100 + s, tile, kb);
@@ -380,14 +387,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const bool issue = p.debug_mode != DEBUG_NO_MMA;
       Ring ring, acc;
       bool ok = true;
-      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
+      for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride, acc.advance(acc_bufs)) {
+        const int tile = unit / split_k, part = unit - tile * split_k;
+        const int kb0 = part * p.kb_per_part, kb1 = min(kb0 + p.kb_per_part, num_k_blocks);
         const uint32_t b = acc.s;
         ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_empty[b]), acc.ph ^ 1u, 200 + b, tile, -1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * static_cast<uint32_t>(acc_cols);
-        for (int kb = 0; kb < num_k_blocks; ++kb, ring.advance(stages)) {
+        for (int kb = kb0; kb < kb1; ++kb, ring.advance(stages)) {
           const uint32_t s = ring.s;
           ok = bounded_wait<false>(wctx, smem_u32(&ctrl->full[s]), ring.ph, 300 + s, tile, kb);
           ok = __all_sync(0xffffffffu, ok);
@@ -410,7 +419,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
                 for (int ns = 0; ns < NS; ++ns)
                   umma_bf16_elect<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n + ns * umma_n), ad,
-                                       bdesc + ns * nsub_step, idesc, (kb | k16) != 0 ? 1u : 0u);
+                                       bdesc + ns * nsub_step, idesc, ((kb - kb0) | k16) != 0 ? 1u : 0u);
               }
             }
           };
@@ -438,7 +447,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t sbuf = 0;
     Ring acc;
     bool ok = true;
-    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, acc.advance(acc_bufs)) {
+    for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride, acc.advance(acc_bufs)) {
+      const int tile = unit / split_k, part = unit - tile * split_k;
       int mt, nt;
       tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
       const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
@@ -465,7 +475,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           tmem_ld_32x32b_x32(taddr + 32u, r1);
           tmem_ld_wait();
           const int col0 = n_base + c * 64;
-          if (row0 < p.M && col0 < p.N) {  // warp-uniform; rows / columns past the edge are clipped by the store
+          if (split_k > 1) {
+            // split-K: this unit's fp32 partial goes to its part's array in the scratch (rows
+            // part * part_rows + ...), 32 columns = one 128-byte staging row at a time; a second
+            // kernel sums the parts.  Same staging buffers and swizzle as the bf16 path.
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (row0 < p.M && col0 + 32 * h < p.N) {
+                const uint32_t buf = stage_base + sbuf * EPI_BUF_BYTES;
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+                const uint32_t sw = static_cast<uint32_t>(lane & 7);
+                const uint32_t* r = h ? r1 : r0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4), r[j * 4], r[j * 4 + 1], r[j * 4 + 2],
+                               r[j * 4 + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                  tma_store_2d(&tm_out, buf, col0 + 32 * h, part * p.part_rows + row0);
+                  tma_store_commit();
+                }
+                sbuf ^= 1u;
+              }
+            }
+          } else if (row0 < p.M && col0 < p.N) {  // warp-uniform; rows / columns past the edge are clipped by the store
             const uint32_t buf = stage_base + sbuf * EPI_BUF_BYTES;
             if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer has drained it
             __syncwarp();

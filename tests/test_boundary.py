@@ -144,6 +144,30 @@ def test_cfg_check_budgets(native_lib):
     print("accepted of the 64-point grid:", accepted, "of the 24 large-tile points:", big.count(native.OK))
 
 
+def test_split_k_validation_and_scratch(native_lib):
+    import ctypes as C
+
+    from autotune import native
+    from autotune.native import Cfg
+
+    pair = dict(tile_m=256, tile_n=256, tile_k=128, stages=3, cluster_m=2)
+    assert native.cfg_check("matmul_lhsT_rhs", dict(pair, split_k=4), 256, 4096, 4096)[0] == native.OK
+    assert native.cfg_check("matmul_lhs_rhs", dict(pair, split_k=16), 256, 4096, 4096)[0] == native.OK
+    assert native.cfg_check("matmul_lhsT_rhs", dict(pair, split_k=17), 256, 4096, 4096)[0] == native.ERR_UNSUPPORTED
+    assert native.cfg_check("rmsnorm_matmul", dict(pair, split_k=2, norm_mode=2), 4096, 4096, 4096)[0] == native.ERR_UNSUPPORTED
+    assert native.cfg_check("rmsnorm_matmul", dict(pair, split_k=2, norm_mode=1), 4096, 4096, 4096)[0] == native.ERR_UNSUPPORTED
+    lib = native.load()
+
+    def ws(fam, c, M, N, K):
+        cc = Cfg.from_dict(c)
+        return lib.b200_workspace_bytes(fam, C.byref(cc), M, N, K)
+
+    assert ws(b"matmul_lhsT_rhs", dict(pair, split_k=4), 256, 4096, 4096) == 4 * 256 * 4096 * 4
+    assert ws(b"matmul_lhsT_rhs", dict(pair, split_k=4), 200, 4096, 4096) == 4 * 256 * 4096 * 4   # rows padded to the tile
+    assert ws(b"matmul_lhsT_rhs", dict(pair, split_k=8), 256, 4096, 256) == 2 * 256 * 4096 * 4    # only 2 k-blocks to deal out
+    assert ws(b"matmul_lhsT_rhs", dict(pair, split_k=1), 256, 4096, 4096) == 0
+
+
 def test_default_candidate_follows_the_problem_size(native_lib):
     """No cfg: large problems get the 512x256 pair tile, short ones a tile that still fills the
     machine; the 16-row fused shape gets the weight-streaming kernel's stage shape."""

@@ -109,6 +109,18 @@ def test_bf16_tall_pair_tiles_two_ummas_along_m(K, k, m, n, c):
     assert _mm_case(K, 10, k, m, n, c) <= TOL_BF16
 
 
+@pytest.mark.parametrize("k,m,n", [(512, 256, 384), (4096, 256, 4096), (520, 1000, 1016), (8192, 128, 512), (192, 136, 72)])
+@pytest.mark.parametrize("c", [dict(cfg(256, 256, 128, 3, cm=2), split_k=4), dict(cfg(128, 128, 64, 4), split_k=3),
+                               dict(cfg(512, 256, 64, 4, cm=2), split_k=2), dict(cfg(256, 128, 64, 3), split_k=16)],
+                         ids=["pair-x4", "1cta-x3", "tall-x2", "msub2-x16"])
+def test_bf16_split_k(K, k, m, n, c):
+    """K range of every tile dealt to several work units, fp32 partials summed by a second kernel."""
+    assert _mm_case(K, 12, k, m, n, c) <= TOL_BF16
+    t = O.generate_inputs(12, [("lhs", (m, k), N_(k)), ("rhs", (k, n), N_(k))], bf16=True)
+    got = K.to_host(K.matmul_lhs_rhs(K.to_device(t["lhs"].astype(BF)), K.to_device(t["rhs"].astype(BF)), cfg=c)).astype(np.float32)
+    assert O.max_abs_rel_err(got, O.matmul_lhs_rhs(t["lhs"], t["rhs"])) <= TOL_BF16
+
+
 def test_bf16_hand_kernel_shape_2048(K, golden):
     """2048^3, the only shape the reference's hand kernel accepts, against its simulated output."""
     t = O.generate_inputs(0, [("lhs_T", (2048, 2048), None), ("rhs", (2048, 2048), None)], bf16=True)
