@@ -67,7 +67,7 @@ struct Plan {
 // Default candidate when the caller passes no b200_cfg.  For the plain GEMM main loop the choice
 // is the candidate with the smallest estimated time: rounds of the persistent schedule (tiles over
 // the CTA groups of a 148-SM part) x tile area per SM / relative throughput of that tile shape
-// as measured at 8192^3.  Large problems get the 512x256 pair tile; short ones a smaller tile that
+// as measured at 4096^3.  Large problems get the 512x256 pair tile; short ones a smaller tile that
 // fills the machine.
 static b200_cfg default_cfg(Family fam, long M, long N) {
   b200_cfg c;
@@ -84,8 +84,11 @@ static b200_cfg default_cfg(Family fam, long M, long N) {
   struct Option { int tile_m, tile_n, tile_k, stages, cluster_m; double rate; };
   static const Option kOptions[] = {
       {512, 256, 64, 4, 2, 1.00},
-      {256, 256, 128, 3, 2, 0.96},
-      {128, 256, 128, 2, 1, 0.76},
+      {256, 256, 128, 3, 2, 0.99},
+      {256, 128, 128, 3, 2, 0.76},
+      {128, 256, 128, 2, 1, 0.74},
+      {128, 128, 128, 3, 1, 0.80},
+      {128, 64, 128, 4, 1, 0.51},
   };
   const Option* best = &kOptions[1];
   if (M > 0 && N > 0) {

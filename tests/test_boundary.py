@@ -181,8 +181,9 @@ def test_default_candidate_follows_the_problem_size(native_lib):
     assert tile("matmul_lhsT_rhs", 8192, 8192, 8192) == (512, 256, 64, 4, 2)
     assert tile("matmul_lhsT_rhs", 131072, 4096, 4096) == (512, 256, 64, 4, 2)
     assert tile("matmul_lhs_rhs", 4096, 11008, 4096) == (512, 256, 64, 4, 2)
-    assert tile("matmul_lhsT_rhs", 256, 4096, 4096) == (256, 256, 128, 3, 2)
-    assert tile("matmul_lhsT_rhs", 512, 512, 512) == (256, 256, 128, 3, 2)
+    assert tile("matmul_lhsT_rhs", 2048, 2048, 2048) == (256, 256, 128, 3, 2)
+    assert tile("matmul_lhsT_rhs", 256, 4096, 4096) == (128, 64, 128, 4, 1)         # 128 tiles for 148 SMs
+    assert tile("matmul_lhsT_rhs", 1024, 8192, 8192) == (512, 256, 64, 4, 2)
     assert tile("rmsnorm_matmul", 16, 28672, 8192)[:1] == (16,)
     assert tile("rmsnorm_matmul", 4096, 11008, 4096) == (128, 256, 128, 2, 1)      # inline variant (no scratch)
     with pytest.raises(native.NativeError):
