@@ -5,11 +5,14 @@
 //   kernel_library/matmul/lhsT_rhs/kernel_hand_90.92mfu.py:72-131  (matmul_block, load_block, store_block)
 // with one fp32 accumulation over the whole of K in tensor memory.
 //
-// Warp roles (one CTA per SM, or a CTA pair sharing one 256-row UMMA):
+// Warp roles (one CTA per SM, or a CTA pair sharing 256-row UMMAs):
 //   warp 0      TMA producer   : waits empty[s], arms full[s], issues the tile loads of stage s
-//   warp 1      UMMA issuer    : waits full[s], issues tile_k/16 UMMAs, commits to empty[s];
-//                                after the last k-block commits acc_full[b]
-//   warps 2-5   epilogue       : wait acc_full[b], tcgen05.ld, bf16, global stores, arrive acc_empty[b]
+//   warp 1      UMMA issuer    : waits full[s], issues tile_k/16 UMMAs per accumulator block, commits
+//                                to empty[s]; after the last k-block commits acc_full[b]
+//   warps 2-5   epilogue       : wait acc_full[b], tcgen05.ld, bf16 into swizzled staging buffers,
+//                                bulk tensor stores, arrive acc_empty[b]
+// Warps 0 and 1 run their loops with all lanes converged and elect one lane per instruction.
+// Work units are (tile, part of the K range); without split-K a unit is a whole tile.
 //
 // Shared-memory operand layout (what the TMA writes and the UMMA descriptors read), with the
 // 128-byte swizzle: an MN-major operand tile [tile_k x W] is W/64 chunks, each chunk = tile_k

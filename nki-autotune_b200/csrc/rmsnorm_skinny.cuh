@@ -8,9 +8,11 @@
 //     shared memory, which only pollutes accumulator rows 16..127 -- rows of D are independent
 //     and those rows are never read.
 //   * stream-K: the (n-tile, k-block) units are flattened and cut into one contiguous range per
-//     CTA, so all SMs stream equal amounts of w whatever N/128 is.  A CTA that covers only part
-//     of a tile's K adds its fp32 partial into a scratch array with atomics; the warp that
-//     completes a tile's count scales by rinv[m], writes bf16 and zeroes the scratch again.
+//     CTA, so all SMs stream equal amounts of w whatever N/256 is.  A CTA that covers only part
+//     of a tile's K publishes its fp32 partial tile in a scratch slot of its own and adds its
+//     k-blocks to the tile's counter; the contributor that completes the count (or finds it
+//     complete but for its own share, in which case it publishes nothing) sums the partials in
+//     CTA order, scales by rinv[m], writes bf16 and resets the counter.
 //   * x is tiny (M*K): four warps stage x*gamma tiles into shared memory in the swizzled
 //     K-major layout the UMMA reads (loads issued one unit ahead), and every CTA computes
 //     rinv[m] for itself from x (L2).
