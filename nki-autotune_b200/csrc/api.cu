@@ -538,7 +538,8 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (plan.prologue) {
     if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0 || (reinterpret_cast<uintptr_t>(la.a) & 15u) != 0)
       return set_error(B200_ERR_BAD_ARG, "workspace must be 256-byte aligned and x 16-byte aligned");
-    rc = make_tmap_bf16(&pr->tm_a, ws, la.M, la.K, la.K, 64, mc, "scaled x (workspace)");
+    if (la.gamma != nullptr) rc = make_tmap_bf16(&pr->tm_a, ws, la.M, la.K, la.K, 64, mc, "scaled x (workspace)");
+    else rc = make_tmap_bf16(&pr->tm_a, la.a, la.M, la.K, la.K, 64, mc, "x");  // no gamma: x is the A operand as it is
   } else if (la.fam == FAM_LHS) {
     rc = make_tmap_bf16(&pr->tm_a, la.a, la.M, la.K, la.ld_a, 64, mc, "lhs");
   } else if (la.fam == FAM_LHST) {
@@ -598,7 +599,7 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   if (plan.prologue) {
     gp.x = static_cast<const __nv_bfloat16*>(la.a);
     gp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
-    gp.xg = reinterpret_cast<__nv_bfloat16*>(ws);
+    gp.xg = la.gamma != nullptr ? reinterpret_cast<__nv_bfloat16*>(ws) : nullptr;  // no gamma: nothing to rewrite
     gp.rinv = reinterpret_cast<float*>(ws + align256(static_cast<size_t>(la.M) * la.K * 2));
     gp.grid_sync = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(gp.rinv) +
                                                    align256(static_cast<size_t>(la.M) * sizeof(float)));

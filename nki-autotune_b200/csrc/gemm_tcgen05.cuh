@@ -228,23 +228,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   if constexpr (NORM) {
     // ---------------------------------------------------------------- prologue: xg, rinv
-    const int warps_total = static_cast<int>(gridDim.x) * (GEMM_THREADS / 32);
+    // gamma is the same for every row: it is staged once in the (still unused) operand stages of
+    // shared memory when it fits, so that the loads in flight are all x (sixteen 16-byte pieces
+    // per lane: the pass is memory-bound and only six warps per SM run it)
     const int pieces = p.K / 8;  // 16-byte pieces per row (K is a multiple of 64)
+    const bool gamma_in_smem = p.gamma != nullptr && static_cast<uint32_t>(p.K) * 2u <= stages * (a_bytes + b_bytes);
+    const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
+    if (gamma_in_smem) {
+      for (int i = threadIdx.x; i < pieces; i += GEMM_THREADS)
+        st_shared_v4(a_base + static_cast<uint32_t>(i) * 16u, __ldg(reinterpret_cast<const uint4*>(p.gamma) + i));
+      __syncthreads();
+    }
+    const int warps_total = static_cast<int>(gridDim.x) * (GEMM_THREADS / 32);
     for (int row = static_cast<int>(blockIdx.x) * (GEMM_THREADS / 32) + warp; row < p.M; row += warps_total) {
       const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K);
       uint4* dst = reinterpret_cast<uint4*>(p.xg + static_cast<long long>(row) * p.K);
       float ss = 0.0f, ss2 = 0.0f;
-      for (int i0 = lane; i0 < pieces; i0 += 128) {  // four independent pieces in flight per lane
-        uint4 v[4], g[4];
+      for (int i0 = lane; i0 < pieces; i0 += 512) {
+        uint4 v[16];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 16; ++u) {
           const int i = i0 + u * 32;
           v[u] = (i < pieces) ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
-          g[u] = (i < pieces && p.gamma != nullptr) ? __ldg(reinterpret_cast<const uint4*>(p.gamma) + i)
-                                                    : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 16; ++u) {
           const int i = i0 + u * 32;
           const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
@@ -253,9 +261,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             ss = fmaf(lo, lo, ss);
             ss2 = fmaf(hi, hi, ss2);
           }
-          if (i < pieces)
-            dst[i] = make_uint4(mul_bf16x2(v[u].x, g[u].x), mul_bf16x2(v[u].y, g[u].y), mul_bf16x2(v[u].z, g[u].z),
-                                mul_bf16x2(v[u].w, g[u].w));
+          if (i < pieces && p.xg != nullptr) {  // without gamma the main loop reads x itself: nothing to write
+            const uint4 g = gamma_in_smem ? ld_shared_v4(a_base + static_cast<uint32_t>(i) * 16u)
+                                          : (p.gamma != nullptr ? __ldg(reinterpret_cast<const uint4*>(p.gamma) + i) : ones);
+            dst[i] = make_uint4(mul_bf16x2(v[u].x, g.x), mul_bf16x2(v[u].y, g.y), mul_bf16x2(v[u].z, g.z),
+                                mul_bf16x2(v[u].w, g.w));
+          }
         }
       }
       ss += ss2;
