@@ -39,7 +39,7 @@ WORKLOAD = "configs[1]: matmul_lhsT_rhs bf16 lhsT[8192,8192] rhs[8192,8192], N(0
 
 # DRAM bytes per launch of the 8192^3 kernel (dram__bytes_read.sum + dram__bytes_write.sum);
 # filled from the ncu capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.005e9  # dram read + write per launch, profiles/gemm_tcgen05_matmul_lhsT_rhs_8192.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.003e9  # dram read + write per launch, profiles/gemm_tcgen05_matmul_lhsT_rhs_8192.md
 
 SHORTLIST = [
     dict(tile_m=512, tile_n=256, tile_k=64, stages=4, cluster_m=2),
