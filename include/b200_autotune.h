@@ -60,10 +60,10 @@ typedef struct b200_cfg {
                      launch first writes x*gamma and rinv to scratch, then runs the plain main
                      loop; needs b200_workspace_bytes of scratch), 0 = prologue when a large
                      enough workspace is passed, else inline                                */
-  int reserved[7]; /* zero in normal use.  Measurement and test hooks: [0] 1 = the TMA producer issues
-                     nothing (makes the consumers' bounded waits run out), 2 = operands loaded once
-                     per stage slot, 3 = UMMAs not issued, 4 = transform work skipped (inline fused
-                     kernel); [1] limit of a device-side wait in microseconds (default 1 s);
+  int reserved[7]; /* zero in normal use.  [0] 1 = test hook: the TMA producer issues nothing, which makes
+                     the consumers' bounded waits run out (values 2..4 are measurement hooks that exist
+                     only in a library built with -DB200_MEASURE_HOOKS and are ignored otherwise);
+                     [1] limit of a device-side wait in microseconds (default 1 s);
                      [2] 1 = GEMM kernel stores its longest CTA lifetime in dev_status[6] (SM cycles)
                      and [7] (nanoseconds)                                                      */
 } b200_cfg;
@@ -130,7 +130,8 @@ int b200_matmul_lhsT_rhs_f32(const void* lhsT, const void* rhs, void* out,
 /* out[M,N] (bf16) = (x / sqrt(mean_k x^2 + eps) * gamma) . w with x[M,K] (K contiguous),
  * gamma[K] (bf16, may be NULL = all ones), w[K,N] (N contiguous); row statistics and
  * accumulation in fp32.  M <= 16 runs the weight-streaming kernel (only tile_k and stages of
- * cfg apply) and needs b200_workspace_bytes of zero-filled scratch; M > 16 see b200_cfg.norm_mode.
+ * cfg apply) and needs b200_workspace_bytes of zero-filled scratch (partial tiles of the
+ * 256-column tiles that are shared between CTAs, and their counters); M > 16 see b200_cfg.norm_mode.
  * Replaces rmsnorm_matmul_online, kernel_library/rmsnorm_matmul/kernel_hand_online.py:198-353
  * (gamma is an extension; gamma == NULL reproduces that kernel's maths). */
 int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out,

@@ -34,10 +34,18 @@ constexpr int GEMM_THREADS = 192;
 constexpr int EPI_BUF_BYTES = 32 * 128;
 constexpr int EPI_STAGE_BYTES = 4 * 2 * EPI_BUF_BYTES;
 
-// measurement / test hooks (b200_cfg.reserved[0])
-constexpr int DEBUG_SKIP_PRODUCER = 1;  // producer issues nothing: the consumers' bounded waits run out
-constexpr int DEBUG_NO_RELOAD = 2;      // operands loaded once per stage slot, then only barriers cycle
-constexpr int DEBUG_NO_MMA = 3;         // loads and barriers run, the UMMAs are not issued
+// test hook (b200_cfg.reserved[0]): the producer issues nothing, so the consumers' bounded waits
+// run out -- how the tests exercise the give-up path without faulting anything
+constexpr int DEBUG_SKIP_PRODUCER = 1;
+// measurement hooks, compiled only into builds made with -DB200_MEASURE_HOOKS (they make the
+// kernels compute garbage on purpose): 2 = operands loaded once per stage slot, then only the
+// barriers cycle; 3 = loads and barriers run, the UMMAs are not issued; 4 = the inline fused
+// kernel's transform warps only cycle their barriers
+#ifdef B200_MEASURE_HOOKS
+constexpr int DEBUG_NO_RELOAD = 2;
+constexpr int DEBUG_NO_MMA = 3;
+constexpr int DEBUG_NO_TRANSFORM = 4;
+#endif
 
 struct GemmParams {
   int M, N, K;
@@ -56,7 +64,7 @@ struct GemmParams {
   int split_k;       // parts the K range of every tile is split into (1 = none); parts are separate work units
   int kb_per_part;   // k-blocks per part
   int part_rows;     // split-K: rows of one part's fp32 partial array (num_m_tiles x tile rows)
-  int debug_mode;    // 0, or one of the DEBUG_* hooks
+  int debug_mode;    // 0, DEBUG_SKIP_PRODUCER, or (measurement builds) one of the other DEBUG_* hooks
   int record_clocks; // measurement aid: status[6]/[7] = longest CTA lifetime in SM cycles / nanoseconds
   // NORM variant only (fused RMSNorm with an in-kernel prologue):
   const __nv_bfloat16* x;      // [M,K] activations
@@ -338,10 +346,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t b_s = b_base + s * b_bytes;
           const int k0 = kb * tile_k;
           const uint32_t full_local = smem_u32(&ctrl->full[s]);
+#ifdef B200_MEASURE_HOOKS
           if (p.debug_mode == DEBUG_NO_RELOAD && it >= static_cast<uint32_t>(stages)) {
-            // measurement aid: operands stay as first loaded, only the barrier protocol runs
+            // operands stay as first loaded, only the barrier protocol runs
             if (!PAIR || cta_rank == 0) mbar_arrive_elect(full_local);
-          } else if constexpr (PAIR) {
+          } else
+#endif
+          if constexpr (PAIR) {
             const uint32_t full_leader = map_to_cta(full_local, 0);
             if (cta_rank == 0) mbar_arrive_expect_tx_elect(full_local, 2u * (a_bytes + b_bytes));
             if constexpr (A_KMAJOR) {
@@ -398,7 +409,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const uint32_t a_step = a_bytes >> 4, b_step = b_bytes >> 4, sub_step = (2u * mn_lbo) >> 4;
       const uint32_t nsub_step = (static_cast<uint32_t>(nc_sub / 64) * mn_lbo) >> 4;  // next UMMA's B chunks
       const int nk16 = tile_k / 16;
+#ifdef B200_MEASURE_HOOKS
       const bool issue = p.debug_mode != DEBUG_NO_MMA;
+#else
+      constexpr bool issue = true;
+#endif
       Ring ring, acc;
       bool ok = true;
       for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride, acc.advance(acc_bufs)) {

@@ -2,20 +2,30 @@
 //     out[M,N] = (x / rms(x) * gamma)[M,K] . w[K,N]
 // The work is streaming w (K*N*2 bytes) once from HBM, so the kernel is built around that:
 //
-//   * one UMMA per 16 k covers 256 weight columns: D[128, 256 n] += A[128, 16 k] . B[16 k, 256 n]
+//   * one UMMA per 16 k covers a tile of 256 weight columns: D[128, 256 n] += A[128, 16 k] . B[16 k, 256 n]
 //     with B = w tile (MN-major, straight from TMA) and A = the scaled x tile (K-major).  Only
 //     rows 0..15 of A exist: the descriptor's row groups beyond them read whatever follows in
 //     shared memory, which only pollutes accumulator rows 16..127 -- rows of D are independent
-//     and those rows are never read.
-//   * stream-K: the (n-tile, k-block) units are flattened and cut into one contiguous range per
-//     CTA, so all SMs stream equal amounts of w whatever N/256 is.  A CTA that covers only part
-//     of a tile's K publishes its fp32 partial tile in a scratch slot of its own and adds its
-//     k-blocks to the tile's counter; the contributor that completes the count (or finds it
-//     complete but for its own share, in which case it publishes nothing) sums the partials in
-//     CTA order, scales by rinv[m], writes bf16 and resets the counter.
+//     and those rows are never read.  Tiles are 256 columns because a k-row of a tile is then 512
+//     contiguous, 512-byte-aligned bytes; narrower or unaligned column strips stream at half the rate.
+//   * work split over G CTAs (one per SM) for T tiles: every CTA takes floor(T / G) whole tiles over
+//     the whole of K (no exchange with anybody).  The R = T mod G tiles left over get one OWNER CTA
+//     each; the other G - R CTAs are DONORS.  An owner streams the last k-blocks of its tile, the
+//     first `don` k-blocks of every left-over tile are dealt to the donors as one flattened range
+//     each.  Donors do their range first and get slightly less work, so every partial tile is in
+//     its scratch slot (and counted) before the owners finish streaming; an owner fetches the
+//     donors' partials while its own k-blocks are still in flight and ends with drain, add, scale,
+//     store, like a CTA that had the tile to itself.  The sum order is fixed (donors in index
+//     order, then the owner), so results do not depend on timing.  Donors have the low CTA
+//     indices: if the grid is ever not co-resident they run first and no owner waits on a CTA
+//     that has not started.
+//   * CTAs start their K loops at different k-blocks (and wrap around): CTAs that walk the same
+//     k-rows at the same time were measured 15 % slower.
 //   * x is tiny (M*K): four warps stage x*gamma tiles into shared memory in the swizzled
 //     K-major layout the UMMA reads (loads issued one unit ahead), and every CTA computes
 //     rinv[m] for itself from x (L2).
+//   * the TMA producer warp initialises the barriers itself and starts loading at once; the
+//     other warps join through a named barrier after the tensor-memory allocation.
 //
 // Same maths as kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 (plus gamma); the
 // per-row factor is applied after the K sum.  All waits are bounded (see gemm_tcgen05.cuh).
@@ -35,12 +45,17 @@ constexpr int SKINNY_SLOT_FLOATS = SKINNY_ROWS * SKINNY_TILE_N;  // one partial 
 struct SkinnyParams {
   int M, N, K;
   int tile_k, stages;
-  int num_n_tiles, num_k_blocks;
+  int num_k_blocks;
+  int base_tiles;               // whole tiles per CTA: tile R + b * base_tiles + i belongs to CTA b
+  int lo_tiles;                 // R: left-over tiles 0..R-1, tile t owned by CTA donors + t
+  int donors;                   // D = gridDim.x - R when R > 0, else 0: CTAs 0..D-1
+  int don;                      // k-blocks 0..don-1 of every left-over tile are streamed by donors
+  int rot;                      // CTA b starts its whole-K loops at k-block (b * rot) mod num_k_blocks
   const __nv_bfloat16* x;
   const __nv_bfloat16* gamma;   // may be nullptr
   __nv_bfloat16* out;
-  float* partial;               // [num_n_tiles + gridDim.x][16][256] fp32 partial tiles, written before read
-  int* tile_count;              // [num_n_tiles] k-blocks contributed so far, all zero between launches
+  float* partial;               // [R + D][16][256] fp32 partial tiles, written before read
+  int* tile_count;              // [R] k-blocks the donors have contributed, all zero between launches
   float eps, inv_k;
   int* status;
   long long timeout_cycles;
@@ -68,6 +83,16 @@ struct SkinnyWait {
   int role;
 };
 
+__device__ __forceinline__ void skinny_give_up(const SkinnyWait& w, int bar_id, int unit) {
+  w.ctrl->abort_flag = 1;
+  if (w.status != nullptr && atomicCAS(w.status, 0, 7) == 0) {
+    w.status[1] = w.role;
+    w.status[2] = bar_id;
+    w.status[3] = unit;
+    w.status[5] = static_cast<int>(blockIdx.x);
+  }
+}
+
 __device__ __forceinline__ bool skinny_wait(const SkinnyWait& w, uint32_t bar, uint32_t parity, int bar_id,
                                             int unit) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -77,19 +102,96 @@ __device__ __forceinline__ bool skinny_wait(const SkinnyWait& w, uint32_t bar, u
     if ((++spins & 63u) == 0u) {
       if (w.ctrl->abort_flag) return false;
       if (clock64() - t0 > w.limit) {
-        w.ctrl->abort_flag = 1;
-        if (w.status != nullptr && atomicCAS(w.status, 0, 7) == 0) {
-          w.status[1] = w.role;
-          w.status[2] = bar_id;
-          w.status[3] = unit;
-          w.status[5] = static_cast<int>(blockIdx.x);
-        }
+        skinny_give_up(w, bar_id, unit);
         return false;
       }
     }
   }
   return true;
 }
+
+enum SkinnyKind { SK_WHOLE = 0, SK_DONATE = 1, SK_OWN = 2 };
+
+// The work of one CTA as a sequence of segments, the same sequence for every role.  A segment is
+// a tile and a range of its k-blocks, walked from kb_start upwards with wrap-around.
+struct SkinnyWork {
+  int nkb, N, b, base, R, D, don, rot;
+  long long du, du_end;   // donor: flattened (left-over tile, donated k-block) units still to hand out
+  int bt;                 // whole tiles handed out so far
+  bool own_pending;       // owner: its left-over tile is still to come
+  // current segment
+  int kind, tile, n0, width;
+  int kb_lo, kb_hi, kb_start;
+  int pos;                // unit-by-unit view: position within the segment
+
+  __device__ __forceinline__ SkinnyWork(const SkinnyParams& p) {
+    nkb = p.num_k_blocks; N = p.N; b = static_cast<int>(blockIdx.x);
+    base = p.base_tiles; R = p.lo_tiles; D = p.donors; don = p.don; rot = p.rot;
+    du = du_end = 0;
+    if (b < D && don > 0) {
+      const long long V = static_cast<long long>(R) * don;
+      du = V * b / D;
+      du_end = V * (b + 1) / D;
+    }
+    bt = 0;
+    own_pending = (b >= D && b - D < R);
+    kind = SK_WHOLE; tile = n0 = width = kb_lo = kb_hi = kb_start = 0;
+    pos = 0;
+  }
+  __device__ __forceinline__ void place(int t) {
+    tile = t;
+    n0 = t * SKINNY_TILE_N;
+    width = min(SKINNY_TILE_N, (N - n0 + 63) & ~63);  // the last chunk may reach past N: the loads fill zeros
+    pos = 0;
+  }
+  __device__ __forceinline__ bool whole_tile() {
+    if (bt >= base) return false;
+    place(R + b * base + bt);
+    kind = SK_WHOLE;
+    kb_lo = 0; kb_hi = nkb;
+    kb_start = static_cast<int>((static_cast<long long>(b) * rot + 7LL * bt) % nkb);
+    ++bt;
+    return true;
+  }
+  __device__ __forceinline__ bool next_segment() {
+    if (b < D) {  // donor: its range of the donated k-blocks first, whole tiles after
+      if (du < du_end) {
+        const int t = static_cast<int>(du / don);
+        place(t);
+        kind = SK_DONATE;
+        kb_lo = static_cast<int>(du - static_cast<long long>(t) * don);
+        const long long seg_end = min(du_end, static_cast<long long>(t + 1) * don);
+        kb_hi = kb_lo + static_cast<int>(seg_end - du);
+        kb_start = kb_lo;
+        du = seg_end;
+        return true;
+      }
+      return whole_tile();
+    }
+    if (whole_tile()) return true;
+    if (own_pending) {  // owner: the rest of its left-over tile last
+      own_pending = false;
+      place(b - D);
+      kind = don > 0 ? SK_OWN : SK_WHOLE;
+      kb_lo = don; kb_hi = nkb;
+      kb_start = don + static_cast<int>((static_cast<long long>(b) * rot) % (nkb - don));
+      return true;
+    }
+    return false;
+  }
+  __device__ __forceinline__ int len() const { return kb_hi - kb_lo; }
+  // k-block at position i of the segment's K loop
+  __device__ __forceinline__ int kb_at(int i) const {
+    const int k = kb_start + i;
+    return k >= kb_hi ? k - (kb_hi - kb_lo) : k;
+  }
+  // unit-by-unit view of the same sequence (k-block of the next unit)
+  __device__ __forceinline__ bool next_unit(int& kb_out) {
+    if (pos >= kb_hi - kb_lo && !next_segment()) return false;
+    kb_out = kb_at(pos++);
+    return true;
+  }
+};
 
 __global__ void __launch_bounds__(SKINNY_THREADS, 1)
 rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyParams p) {
@@ -109,35 +211,46 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   uint8_t* const smem_gen = smem_raw - smem_u32(smem_raw);
   SkinnyCtrl* ctrl = reinterpret_cast<SkinnyCtrl*>(smem_gen + ctrl_addr);
 
-  // this CTA's contiguous range of (n-tile, k-block) units
-  const int nkb = p.num_k_blocks;
-  const long long total_units = static_cast<long long>(p.num_n_tiles) * nkb;
-  const long long u_begin = total_units * blockIdx.x / gridDim.x;
-  const long long u_end = total_units * (blockIdx.x + 1) / gridDim.x;
-
-  if (threadIdx.x == 0) {
-    ctrl->abort_flag = 0;
-    tma_prefetch_desc(&tm_w);
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&ctrl->full_w[s]), 1);
-      mbar_init(smem_u32(&ctrl->full_x[s]), 4);
-      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+  // ------------------------------------------------------------------ set-up
+  // The producer warp initialises the barriers and goes straight to its loads (it needs nothing
+  // else); the other nine warps wait for that and for the tensor-memory allocation at a named
+  // barrier the producer only arrives at.
+  if (warp == 0) {
+    if (lane == 0) {
+      ctrl->abort_flag = 0;
+      tma_prefetch_desc(&tm_w);
+      for (int s = 0; s < stages; ++s) {
+        mbar_init(smem_u32(&ctrl->full_w[s]), 1);
+        mbar_init(smem_u32(&ctrl->full_x[s]), 4);
+        mbar_init(smem_u32(&ctrl->empty[s]), 1);
+      }
+      for (int b = 0; b < SKINNY_ACC_BUFS; ++b) {
+        mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
+        mbar_init(smem_u32(&ctrl->acc_empty[b]), 1);
+      }
+      fence_mbar_init();
+      fence_proxy_async_smem();
     }
-    for (int b = 0; b < SKINNY_ACC_BUFS; ++b) {
-      mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[b]), 1);
+    __syncwarp();
+    asm volatile("bar.arrive 2, %0;" ::"n"(SKINNY_THREADS) : "memory");
+  } else {
+    if (warp == 1) {
+      tmem_alloc<1>(smem_u32(&ctrl->tmem_base), SKINNY_TMEM_COLS);
+      tmem_relinquish<1>();
     }
-    fence_mbar_init();
+    tc_fence_before();
+    asm volatile("bar.sync 2, %0;" ::"n"(SKINNY_THREADS) : "memory");
+    tc_fence_after();
   }
-  if (warp == 1) {
-    tmem_alloc<1>(smem_u32(&ctrl->tmem_base), SKINNY_TMEM_COLS);
-    tmem_relinquish<1>();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = ctrl->tmem_base;
   SkinnyWait wctx{ctrl, p.status, p.timeout_cycles, 0};
+#ifdef B200_MEASURE_HOOKS
+  // measurement build only: per-CTA globaltimer stamps in the last partial-tile slot of the scratch
+  // ([0] entry, [2] first weight tile landed, [3] last accumulator committed, [4] seen by the
+  // epilogue, [5] epilogue done, [6] donors' partials fetched, [7] rinv done)
+  unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.partial + static_cast<size_t>((p.N + 255) / 256 + SKINNY_MAX_CTAS - 1) * SKINNY_SLOT_FLOATS) + blockIdx.x * 8;
+  if (threadIdx.x == 0) trace[0] = global_timer_ns();
+  if (threadIdx.x == 32) trace[1] = global_timer_ns();
+#endif
 
   // ------------------------------------------------------------------ TMA producer (w tiles)
   // producer and issuer loops run with all lanes converged; one elected lane issues each copy,
@@ -147,18 +260,23 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       wctx.role = ROLE_PRODUCER;
       Ring ring;
       bool ok = true;
-      int nt = static_cast<int>(u_begin / nkb);
-      int kb = static_cast<int>(u_begin - static_cast<long long>(nt) * nkb);
-      for (long long u = u_begin; u < u_end && ok; ++u, ring.advance(stages)) {
-        ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 100 + ring.s, static_cast<int>(u - u_begin));
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const uint32_t w_s = w_base + ring.s * w_bytes;
-        const uint32_t fw = smem_u32(&ctrl->full_w[ring.s]);
-        mbar_arrive_expect_tx_elect(fw, w_bytes);
-        for (int c = 0; c < SKINNY_TILE_N / 64; ++c)
-          tma_load_2d_elect(w_s + c * tile_k * 128, &tm_w, fw, nt * SKINNY_TILE_N + 64 * c, kb * tile_k);
-        if (++kb == nkb) { kb = 0; ++nt; }
+      int unit = 0;
+      SkinnyWork work(p);
+      while (ok && work.next_segment()) {
+        const int chunks = work.width / 64;
+        const uint32_t seg_bytes = static_cast<uint32_t>(work.width) * tile_k * 2u;
+        const int len = work.len();
+        for (int i = 0; i < len; ++i, ++unit, ring.advance(stages)) {
+          ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 100 + ring.s, unit);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const uint32_t w_s = w_base + ring.s * w_bytes;
+          const uint32_t fw = smem_u32(&ctrl->full_w[ring.s]);
+          const int k0 = work.kb_at(i) * tile_k;
+          mbar_arrive_expect_tx_elect(fw, seg_bytes);
+          for (int c = 0; c < chunks; ++c)
+            tma_load_2d_elect(w_s + c * tile_k * 128, &tm_w, fw, work.n0 + 64 * c, k0);
+        }
       }
       for (int i = 0; i < stages && ok; ++i, ring.advance(stages)) {
         ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 150 + ring.s, -1);
@@ -171,29 +289,33 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   else if (warp == 1) {
     {
       wctx.role = ROLE_MMA;
-      const uint32_t idesc = make_idesc_bf16_f32(128, SKINNY_TILE_N, 0, 1);  // A K-major, B MN-major
+      const uint32_t tmem_base = ctrl->tmem_base;
       const uint32_t mn_lbo = static_cast<uint32_t>(tile_k) * 128u;
       const uint64_t b_desc0 = make_smem_desc_sw128(w_base, mn_lbo, 1024);
       const int nk16 = tile_k / 16;
       Ring ring, acc;
       bool ok = true;
-      long long u = u_begin;
-      while (u < u_end && ok) {
-        const int nt = static_cast<int>(u / nkb);
-        const long long seg_end = min(u_end, static_cast<long long>(nt + 1) * nkb);
-        ok = skinny_wait(wctx, smem_u32(&ctrl->acc_empty[acc.s]), acc.ph ^ 1u, 200 + acc.s, static_cast<int>(u - u_begin));
+      int unit = 0;
+      SkinnyWork work(p);
+      while (ok && work.next_segment()) {
+        const uint32_t idesc = make_idesc_bf16_f32(128, work.width, 0, 1);  // A K-major, B MN-major
+        ok = skinny_wait(wctx, smem_u32(&ctrl->acc_empty[acc.s]), acc.ph ^ 1u, 200 + acc.s, unit);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc.s * SKINNY_TILE_N;
         bool first = true;
-        for (; u < seg_end; ++u, ring.advance(stages)) {
+        const int len = work.len();
+        for (int i = 0; i < len; ++i, ++unit, ring.advance(stages)) {
           const uint32_t s = ring.s;
-          ok = skinny_wait(wctx, smem_u32(&ctrl->full_w[s]), ring.ph, 300 + s, static_cast<int>(u - u_begin));
+          ok = skinny_wait(wctx, smem_u32(&ctrl->full_w[s]), ring.ph, 300 + s, unit);
           ok = __all_sync(0xffffffffu, ok);
-          if (ok) ok = skinny_wait(wctx, smem_u32(&ctrl->full_x[s]), ring.ph, 400 + s, static_cast<int>(u - u_begin));
+          if (ok) ok = skinny_wait(wctx, smem_u32(&ctrl->full_x[s]), ring.ph, 400 + s, unit);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+#ifdef B200_MEASURE_HOOKS
+          if (lane == 0 && unit == 0) trace[2] = global_timer_ns();
+#endif
           tc_fence_after();
           uint64_t bdesc = b_desc0 + s * (w_bytes >> 4);
           const uint32_t x_s = x_base + s * x_bytes;
@@ -208,7 +330,9 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
         if (!ok) break;
         umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[acc.s]));
         acc.advance(SKINNY_ACC_BUFS);
-
+#ifdef B200_MEASURE_HOOKS
+        if (lane == 0) trace[3] = global_timer_ns();
+#endif
       }
     }
     __syncwarp();
@@ -216,154 +340,193 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   // ------------------------------------------------------------------ epilogue warps
   else if (warp < 6) {
     wctx.role = ROLE_EPILOGUE;
+    const uint32_t tmem_base = ctrl->tmem_base;
     const int q = warp & 3;          // tensor-memory lane quadrant
     const int et = (warp - 2) * 32 + lane;  // 0..127
     // rinv[m] for every row, from x itself: 8 threads per row, 16-byte loads, shuffle reduction
     {
       const int row = et >> 3, part = et & 7;
-      float ss = 0.0f;
+      float ss = 0.0f, ss2 = 0.0f;
       if (row < p.M) {
         const int per = p.K / 8;  // K is a multiple of 64
         const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K + part * per);
-        for (int i0 = 0; i0 < per / 8; i0 += 8) {  // eight independent 16-byte loads in flight
-          uint4 v8[8];
+        for (int i0 = 0; i0 < per / 8; i0 += 32) {  // 32 independent 16-byte loads in flight
+          uint4 v16[32];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v8[i] = (i0 + i < per / 8) ? __ldg(src + i0 + i) : make_uint4(0u, 0u, 0u, 0u);
+          for (int i = 0; i < 32; ++i) v16[i] = (i0 + i < per / 8) ? __ldg(src + i0 + i) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t w4[4] = {v8[i].x, v8[i].y, v8[i].z, v8[i].w};
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t w4[4] = {v16[i].x, v16[i].y, v16[i].z, v16[i].w};
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
               const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
               ss = fmaf(lo, lo, ss);
-              ss = fmaf(hi, hi, ss);
+              ss2 = fmaf(hi, hi, ss2);
             }
           }
         }
       }
+      ss += ss2;
       ss += __shfl_xor_sync(0xffffffffu, ss, 1);
       ss += __shfl_xor_sync(0xffffffffu, ss, 2);
       ss += __shfl_xor_sync(0xffffffffu, ss, 4);
       if (part == 0) ctrl->rinv[row] = (row < p.M) ? rsqrtf(ss * p.inv_k + p.eps) : 0.0f;
       // the four epilogue warps meet here once, before any bounded wait (no early exit possible)
       asm volatile("bar.sync 1, 128;" ::: "memory");
+#ifdef B200_MEASURE_HOOKS
+      if (et == 0) trace[7] = global_timer_ns();
+#endif
     }
-    // Accumulator rows 0..15 (tensor-memory lanes 0..15) hold the result; only the warp that owns
-    // lane quadrant 0 can read them, so it alone drains: lane m holds out[m, n0 .. n0+255].
+    // Accumulator rows 0..15 (tensor-memory lanes 0..15) hold the result and only the warp that owns
+    // lane quadrant 0 can read them, so it alone drains them, to a staging tile in shared memory
+    // (lane m holds out[m, n0 .. n0 + width): stores straight from that layout would put 16
+    // different rows into every instruction).  Everything row-wise -- fetching the donors'
+    // partials, publishing a partial, scaling and storing the result, 512 bytes per instruction
+    // -- is shared by the four warps, four rows each.  The warps meet at named barrier 1; the
+    // other three never wait on anything else, and every exit from the loop is taken by all four
+    // right after a barrier.
+    static_assert(SKINNY_TILE_N == 256 && SKINNY_ROWS == 16, "row-wise passes cover 2 x 128 columns, 4 x 4 rows");
+    auto epi_sync = []() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+    const int r0 = q * 4;  // first of this warp's rows in the row-wise passes
     Ring acc;
-    bool ok = (q == 0);
-    long long u = u_begin;
-    while (u < u_end && ok) {
-      const int nt = static_cast<int>(u / nkb);
-      const long long seg_end = min(u_end, static_cast<long long>(nt + 1) * nkb);
-      const int seg_blocks = static_cast<int>(seg_end - u);
-      ok = skinny_wait(wctx, smem_u32(&ctrl->acc_full[acc.s]), acc.ph, 500 + acc.s, static_cast<int>(u - u_begin));
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int n0 = nt * SKINNY_TILE_N;
-      const bool whole_k = (seg_blocks == nkb);  // this CTA summed the tile's whole K range
-      // Lane m holds row m of the accumulator.  Stores straight from that layout would put 16
-      // different rows into every instruction, so the tile first goes to shared memory (which also
-      // frees the accumulator early); everything after reads it row-wise, 512 bytes per instruction.
-      for (int c = 0; c < SKINNY_TILE_N / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + acc.s * SKINNY_TILE_N + c * 32, v);
-        tmem_ld_wait();
-        if (lane < SKINNY_ROWS) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(&ctrl->tile_s[lane][c * 32 + j * 4]) =
-                make_uint4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+    int unit = 0;
+    SkinnyWork work(p);
+    while (work.next_segment()) {
+      const int nt = work.tile;
+      const int kind = work.kind;
+      const int width = work.width;
+      const int n0 = work.n0;
+      // columns of the tile this lane touches in the row-wise passes: j * 128 + lane * 4, j = 0, 1
+      const bool col_ok[2] = {lane * 4 < width, 128 + lane * 4 < width};
+      if (kind == SK_OWN) {
+        // The donors' partials are on their way (or there already) while this CTA's own k-blocks
+        // stream.  Wait for the count (bounded like every wait), then their sum, in donor order,
+        // goes to the staging tile.
+        if (q == 0) {
+          const long long t0 = clock64();
+          for (;;) {
+            int seen = 0;
+            if (lane == 0) seen = ld_acquire_gpu(p.tile_count + nt);
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            if (seen == p.don || ctrl->abort_flag) break;
+            if (clock64() - t0 > wctx.limit) { skinny_give_up(wctx, 600, nt); break; }
+            __nanosleep(200);
+          }
         }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[acc.s]));
-      static_assert(SKINNY_TILE_N == 256 && SKINNY_ROWS == 16, "row-wise passes cover 2 x 128 columns, 2 x 8 rows");
-      const long long G = gridDim.x;
-      bool last = whole_k;
-      if (!whole_k) {
-        // Contributors publish their partial tile (slot index = CTA index + tile index, unique along
-        // the chain of K ranges) and then add their k-blocks to the tile's counter; whoever brings
-        // it to nkb sums up.  A contributor that finds all the others already counted is known to
-        // be the last without publishing anything: its own partial stays in shared memory.
-        int before = 0;
-        if (lane == 0) before = ld_acquire_gpu(p.tile_count + nt);
-        before = __shfl_sync(0xffffffffu, before, 0);
-        last = (before + seg_blocks == nkb);
-        if (!last) {
-          float* const slot = p.partial + static_cast<size_t>(blockIdx.x + nt) * SKINNY_SLOT_FLOATS;
+        epi_sync();
+        if (ctrl->abort_flag) break;
+        __threadfence();  // the donors' partials are visible from here on
+        const long long V = static_cast<long long>(p.lo_tiles) * p.don;
+        const int d_lo = static_cast<int>(((static_cast<long long>(nt) * p.don + 1) * p.donors - 1) / V);
+        const int d_hi = static_cast<int>(((static_cast<long long>(nt + 1) * p.don) * p.donors - 1) / V);
+        float4 v[4][2];
 #pragma unroll
-          for (int m = 0; m < SKINNY_ROWS; ++m)
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) v[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int d = d_lo; d <= d_hi; ++d) {
+          if (V * d / p.donors == V * (d + 1) / p.donors) continue;  // a donor without units
+          const float* other = p.partial + static_cast<size_t>(d + nt) * SKINNY_SLOT_FLOATS;
+          float4 t[4][2];  // 8 independent 16-byte loads in flight per lane
+#pragma unroll
+          for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              __stcg(reinterpret_cast<float4*>(slot + m * SKINNY_TILE_N + j * 128 + lane * 4),
-                     *reinterpret_cast<const float4*>(&ctrl->tile_s[m][j * 128 + lane * 4]));
-          __threadfence();
-          __syncwarp();
-          int seen = 0;
-          if (lane == 0) seen = atomicAdd(p.tile_count + nt, seg_blocks) + seg_blocks;
-          seen = __shfl_sync(0xffffffffu, seen, 0);
-          last = (seen == nkb);  // the others finished in the meantime
-        }
-        if (last) __threadfence();  // the other contributors' partials are visible from here on
-      }
-      if (last) {
-        // sum of the contributors' partials in CTA order, whoever does the summing (the result does
-        // not depend on which contributor came last): this CTA's from shared memory, the others'
-        // from their slots, found from the same partition arithmetic; scale, store, and leave the
-        // counter zero for the next launch
-        int c_lo = static_cast<int>(blockIdx.x), c_hi = static_cast<int>(blockIdx.x);
-        if (!whole_k) {
-          c_lo = static_cast<int>(((static_cast<long long>(nt) * nkb + 1) * G - 1) / total_units);
-          c_hi = static_cast<int>(((static_cast<long long>(nt + 1) * nkb) * G - 1) / total_units);
-        }
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          float4 v[8][2];
+              t[r][j] = col_ok[j] ? __ldcg(reinterpret_cast<const float4*>(other + (r0 + r) * SKINNY_TILE_N + j * 128 + lane * 4))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int r = 0; r < 8; ++r)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) v[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int cc = c_lo; cc <= c_hi; ++cc) {
-            if (total_units * cc / G == total_units * (cc + 1) / G) continue;     // a CTA with no units
-            const bool mine = (cc == static_cast<int>(blockIdx.x));
-            const float* other = p.partial + static_cast<size_t>(cc + nt) * SKINNY_SLOT_FLOATS;
-            // 16 independent 16-byte loads in flight per lane (8 rows x 2 column groups)
-            float4 t[8][2];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-#pragma unroll
-              for (int j = 0; j < 2; ++j)
-                t[r][j] = mine ? *reinterpret_cast<const float4*>(&ctrl->tile_s[half * 8 + r][j * 128 + lane * 4])
-                               : __ldcg(reinterpret_cast<const float4*>(other + (half * 8 + r) * SKINNY_TILE_N + j * 128 + lane * 4));
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                v[r][j].x += t[r][j].x; v[r][j].y += t[r][j].y; v[r][j].z += t[r][j].z; v[r][j].w += t[r][j].w;
-              }
-          }
-#pragma unroll
-          for (int r = 0; r < 8; ++r)
+          for (int r = 0; r < 4; ++r)
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-              const int m = half * 8 + r, nn = n0 + j * 128 + lane * 4;
-              if (m < p.M && nn < p.N) {  // N is a multiple of 8: a group of four columns never straddles N
-                const float ri = ctrl->rinv[m];
-                uint2 o;
-                o.x = pack_bf16x2(v[r][j].x * ri, v[r][j].y * ri);
-                o.y = pack_bf16x2(v[r][j].z * ri, v[r][j].w * ri);
-                *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + nn) = o;
-              }
+              v[r][j].x += t[r][j].x; v[r][j].y += t[r][j].y; v[r][j].z += t[r][j].z; v[r][j].w += t[r][j].w;
             }
         }
-        if (!whole_k && lane == 0) p.tile_count[nt] = 0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            *reinterpret_cast<float4*>(&ctrl->tile_s[r0 + r][j * 128 + lane * 4]) = v[r][j];
+        if (et == 0) p.tile_count[nt] = 0;  // zero again for the next launch
+        epi_sync();
+#ifdef B200_MEASURE_HOOKS
+        if (et == 0) trace[6] = global_timer_ns();
+#endif
       }
-      __syncwarp();  // the next segment's drain overwrites the staging tile
-      u = seg_end;
+      if (q == 0) {
+        bool ok = skinny_wait(wctx, smem_u32(&ctrl->acc_full[acc.s]), acc.ph, 500 + acc.s, unit);
+        ok = __all_sync(0xffffffffu, ok);
+#ifdef B200_MEASURE_HOOKS
+        if (lane == 0) trace[4] = global_timer_ns();
+#endif
+        if (ok) {
+          tc_fence_after();
+          // the accumulator goes to the staging tile (an owner adds it to the donors' sum that is
+          // already there), which also frees it early for the issuer
+          for (int c = 0; c < width / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tmem_base + acc.s * SKINNY_TILE_N + c * 32, v);
+            tmem_ld_wait();
+            if (lane < SKINNY_ROWS) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4* dst = reinterpret_cast<float4*>(&ctrl->tile_s[lane][c * 32 + j * 4]);
+                float4 a = make_float4(__uint_as_float(v[j * 4]), __uint_as_float(v[j * 4 + 1]),
+                                       __uint_as_float(v[j * 4 + 2]), __uint_as_float(v[j * 4 + 3]));
+                if (kind == SK_OWN) {
+                  const float4 o = *dst;
+                  a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w;
+                }
+                *dst = a;
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[acc.s]));
+        }
+      }
+      unit += work.len();
+      epi_sync();
+      if (ctrl->abort_flag) break;
+      if (kind == SK_DONATE) {
+        // publish the partial tile (slot index = donor index + tile index, unique along the chain of
+        // donated ranges), then add the k-blocks to the tile's counter
+        float* const slot = p.partial + static_cast<size_t>(blockIdx.x + nt) * SKINNY_SLOT_FLOATS;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            if (col_ok[j])
+              __stcg(reinterpret_cast<float4*>(slot + (r0 + r) * SKINNY_TILE_N + j * 128 + lane * 4),
+                     *reinterpret_cast<const float4*>(&ctrl->tile_s[r0 + r][j * 128 + lane * 4]));
+        __threadfence();
+        epi_sync();
+        if (et == 0) {
+          __threadfence();
+          atomicAdd(p.tile_count + nt, work.len());
+        }
+      } else {
+        // scale by rinv[m], round, store
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int m = r0 + r, nn = n0 + j * 128 + lane * 4;
+            if (m < p.M && col_ok[j] && nn < p.N) {  // N is a multiple of 8: a group of four columns never straddles N
+              const float4 v = *reinterpret_cast<const float4*>(&ctrl->tile_s[m][j * 128 + lane * 4]);
+              const float ri = ctrl->rinv[m];
+              uint2 o;
+              o.x = pack_bf16x2(v.x * ri, v.y * ri);
+              o.y = pack_bf16x2(v.z * ri, v.w * ri);
+              *reinterpret_cast<uint2*>(p.out + static_cast<long long>(m) * p.N + nn) = o;
+            }
+          }
+        epi_sync();  // the next segment's passes overwrite the staging tile
+      }
       acc.advance(SKINNY_ACC_BUFS);
+#ifdef B200_MEASURE_HOOKS
+      if (et == 0) trace[5] = global_timer_ns();
+#endif
     }
   }
   // ------------------------------------------------------------------ x-tile staging warps
@@ -374,11 +537,9 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
     const int pieces = SKINNY_ROWS * pieces_per_row;  // 128 (tile_k 64) or 256 (tile_k 128)
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
     const uint4 one4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
-    // x and gamma pieces of unit u; loads are issued one unit ahead of their use so that the
+    // x and gamma pieces of k-block kb; loads are issued one unit ahead of their use so that the
     // L2 latency overlaps the previous stage instead of adding to every stage
-    auto load_unit = [&](long long u, uint4 (&xv)[2], uint4 (&gv)[2]) {
-      const int nt = static_cast<int>(u / nkb);
-      const int kb = static_cast<int>(u - static_cast<long long>(nt) * nkb);
+    auto load_unit = [&](int kb, uint4 (&xv)[2], uint4 (&gv)[2]) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int c = tt + i * 128;
@@ -395,12 +556,16 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       }
     };
     uint4 cur_x[2], cur_g[2], nxt_x[2], nxt_g[2];
-    if (u_begin < u_end) load_unit(u_begin, cur_x, cur_g);
+    SkinnyWork work(p);
+    int kb_next = 0;
+    bool have = work.next_unit(kb_next);
+    if (have) load_unit(kb_next, cur_x, cur_g);
     Ring ring;
     bool ok = true;
-    for (long long u = u_begin; u < u_end && ok; ++u, ring.advance(stages)) {
-      if (u + 1 < u_end) load_unit(u + 1, nxt_x, nxt_g);
-      ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 700 + ring.s, static_cast<int>(u - u_begin));
+    for (int unit = 0; have && ok; ++unit, ring.advance(stages)) {
+      const bool more = work.next_unit(kb_next);
+      if (more) load_unit(kb_next, nxt_x, nxt_g);
+      ok = skinny_wait(wctx, smem_u32(&ctrl->empty[ring.s]), ring.ph ^ 1u, 700 + ring.s, unit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* x_s = smem_gen + x_base + ring.s * x_bytes;
@@ -424,6 +589,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->full_x[ring.s]));
 #pragma unroll
       for (int i = 0; i < 2; ++i) { cur_x[i] = nxt_x[i]; cur_g[i] = nxt_g[i]; }
+      have = more;
     }
   }
 
@@ -436,7 +602,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, SKINNY_TMEM_COLS);
+    tmem_dealloc<1>(ctrl->tmem_base, SKINNY_TMEM_COLS);
   }
 }
 

@@ -50,10 +50,9 @@ struct RmsParams {
   const __nv_bfloat16* gamma;
   int* status;
   long long timeout_cycles;
-  int debug_mode;  // 0, DEBUG_NO_MMA, or DEBUG_NO_TRANSFORM (measurement hooks)
+  int debug_mode;  // 0, or (measurement builds) DEBUG_NO_MMA / DEBUG_NO_TRANSFORM
 };
 
-constexpr int DEBUG_NO_TRANSFORM = 4;  // transform warps only cycle the barriers
 
 struct alignas(16) RmsCtrl {
   uint64_t full_a[MAX_STAGES];
@@ -298,7 +297,9 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
           for (int k16 = 0; k16 < nk16; ++k16, bdesc += 128, a_tmem += 8) {
 #pragma unroll
             for (int mi = 0; mi < M_SUB; ++mi)
+#ifdef B200_MEASURE_HOOKS
               if (p.debug_mode != DEBUG_NO_MMA)
+#endif
                 umma_bf16_ts_elect<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n),
                                       a_tmem + static_cast<uint32_t>(mi * (tile_k / 2)), bdesc, idesc,
                                       (kb | k16) != 0 ? 1u : 0u);
@@ -417,7 +418,12 @@ rmsnorm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         tc_fence_after();
         const uint8_t* a_s = smem_gen + a_base + s * a_bytes;
         const int k0 = kb * tile_k;
-        for (int grp = 0; grp < (p.debug_mode == DEBUG_NO_TRANSFORM ? 0 : tile_k / 32); ++grp) {
+#ifdef B200_MEASURE_HOOKS
+        const int n_grp = p.debug_mode == DEBUG_NO_TRANSFORM ? 0 : tile_k / 32;
+#else
+        const int n_grp = tile_k / 32;
+#endif
+        for (int grp = 0; grp < n_grp; ++grp) {
           const int e0 = grp * 32;        // first k element (within the stage) of this group of 32
           const int chunk = e0 >> 6;      // 64-wide shared-memory chunk
           const int j0 = (e0 & 63) >> 3;  // first 16-byte piece within the row

@@ -282,6 +282,20 @@ def test_rmsnorm_skinny_shapes(K, m, k, n, c):
         assert O.max_abs_rel_err(got, expect) <= TOL_BF16
 
 
+@pytest.mark.parametrize("m,k,n", [
+    (16, 256, 37888),   # 148 tiles on 148 SMs: one whole tile per CTA, nothing shared
+    (16, 128, 40000),   # whole tiles plus a few left-over tiles with owners and donors; ragged last tile
+    (4, 192, 9472),     # K not a multiple of the 128-deep stage; fewer tiles than SMs
+    (16, 8192, 512),    # two tiles, every CTA a donor or an owner of a long K range
+])
+def test_rmsnorm_skinny_work_splits(K, m, k, n):
+    """Shapes that exercise every branch of the tile split of the weight-streaming kernel (whole
+    tiles only, whole tiles + shared left-over tiles, shared tiles only), twice on one scratch."""
+    for _ in range(2):
+        got, expect = _rms_case(K, 23, m, k, n, 1e-5, None)
+        assert O.max_abs_rel_err(got, expect) <= TOL_BF16
+
+
 def test_rmsnorm_skinny_counters_are_left_zero_and_slots_need_no_clearing(K):
     """The scratch starts with one counter per 256-column tile (zero between launches); the
     partial-tile slots behind them are written before they are read, so stale contents are harmless."""
