@@ -65,7 +65,9 @@ typedef struct b200_cfg {
                      only in a library built with -DB200_MEASURE_HOOKS and are ignored otherwise);
                      [1] limit of a device-side wait in microseconds (default 1 s);
                      [2] 1 = GEMM kernel stores its longest CTA lifetime in dev_status[6] (SM cycles)
-                     and [7] (nanoseconds)                                                      */
+                     and [7] (nanoseconds); [3] > 0 = cap on the GEMM kernels' grid in CTAs (the
+                     persistent schedule deals the tiles to fewer CTAs), for callers that run
+                     another kernel, e.g. a collective, beside it                              */
 } b200_cfg;
 
 /* Number of ints in a dev_status block (device memory, caller-owned, zeroed by caller).

@@ -246,16 +246,22 @@ def time_kernel(
     ms = (C.c_float * iters)()
     c = Cfg.from_dict(cfg)
     ws = workspace_for(family, M, N, K, a.device, cfg)
-    native.check(
-        lib.b200_time_kernel(
-            C.byref(prob), C.byref(c) if c is not None else None,
-            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-            status.data_ptr() if status is not None else None,
-            flush.data_ptr() if flush is not None else None,
-            flush.numel() * flush.element_size() if flush is not None else 0,
-            warmup, iters, ms, _stream_ptr(),
-        )
+    rc = lib.b200_time_kernel(
+        C.byref(prob), C.byref(c) if c is not None else None,
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+        status.data_ptr() if status is not None else None,
+        flush.data_ptr() if flush is not None else None,
+        flush.numel() * flush.element_size() if flush is not None else 0,
+        warmup, iters, ms, _stream_ptr(),
     )
+    if rc == native.ERR_DEVICE_WAIT:
+        # a launch gave up on a device-side wait: whatever scratch it used (counters, partial
+        # tiles) is undefined now, and the cached buffers would poison every later candidate
+        message = native.last_error()
+        torch.cuda.synchronize()
+        reset_workspaces()
+        raise NativeError(rc, message)
+    native.check(rc)
     return list(ms)
 
 

@@ -40,6 +40,7 @@ class Cfg(C.Structure):
         cfg.reserved[0] = int(d.get("_debug_mode", d.get("_debug_skip_producer", 0)))
         cfg.reserved[1] = int(d.get("_wait_limit_us", 0))
         cfg.reserved[2] = int(d.get("_record_clocks", 0))
+        cfg.reserved[3] = int(d.get("_max_ctas", 0))
         return cfg
 
 

@@ -27,10 +27,11 @@ def profile(
     neuron_platform_target: str,
     collect_detailed_profile: bool,
     n_gpus: int | None = None,
-    warmup: int = 3,
-    iters: int = 10,
+    warmup: int = 10,
+    iters: int = 50,
     shard: tuple[int, int] | None = None,
     retime_top: int = 0,
+    inputs: dict | None = None,
 ) -> ProfileOutput:
     """Validate and time a set of candidates on the GPUs of this box.
 
@@ -44,11 +45,14 @@ def profile(
             drivers run unchanged.
         collect_detailed_profile: Attach the per-launch timing list as ``profile.json``.
         n_gpus: Optional cap on the number of GPUs the sweep is sharded over (extension).
-        warmup, iters: Untimed and timed launches per candidate (extension).
+        warmup, iters: Untimed and timed launches per candidate; the reported time is the median
+            of the timed ones (extension).
         shard: ``(rank, world)`` when the caller already runs one process per GPU; this
             process then times only its share of the candidates (extension).
         retime_top: After a sweep sharded over several GPUs, time the fastest ``retime_top``
             candidates again on one GPU so that the leaders are ranked on one device (extension).
+        inputs: Input arrays by tensor name, if the caller already holds what ``seed`` and the
+            specs would generate; nothing is generated then (extension).
 
     Returns:
         ``ProfileOutput`` with every candidate present, as a success or as a failure row.
@@ -72,6 +76,7 @@ def profile(
         iters=iters,
         shard=shard,
         retime_top=retime_top,
+        inputs=inputs,
     )
     elapsed_s = time.monotonic() - start
     logger.info("Profile complete: %d results in %.1fs", len(results), elapsed_s)

@@ -120,8 +120,8 @@ def benchmark_one(
     batch: DeviceBatch,
     cr: CompileResult,
     candidate: Candidate,
-    warmup: int = 3,
-    iters: int = 10,
+    warmup: int = 10,
+    iters: int = 50,
     collect_detailed_profile: bool = False,
 ) -> ProfileResult:
     """Time one validated candidate and check its output; never raises (reference: benchmark.py:116-153)."""

@@ -57,7 +57,13 @@ def compile_one(
         if input_dtype_name == "float32":
             log_lines.append("fp32 inputs: CUDA-core kernel; tile meta-parameters do not apply to it")
         else:
-            status, message, smem, tmem = native.cfg_check(func_name, cand.config, M, N, K)
+            config = dict(cand.config)
+            if func_name == "rmsnorm_matmul" and M > 16 and int(config.get("norm_mode", 0) or 0) == 0:
+                # the timing path always hands the kernel its scratch, and with scratch the library
+                # resolves norm_mode 0 to the prologue variant: validate the plan that will run
+                config["norm_mode"] = 2
+                log_lines.append("norm_mode 0 with scratch supplied: validated as norm_mode 2 (prologue variant)")
+            status, message, smem, tmem = native.cfg_check(func_name, config, M, N, K)
             log_lines.append(f"shared memory {smem} B of 232448 B; tensor memory {tmem} of 512 columns")
             if status != native.OK:
                 error = message

@@ -76,11 +76,73 @@ def shard_round_robin(items: list, n_workers: int) -> list[list]:
 
 
 # ----------------------------------------------------------------------------- GPU worker body
+def batch_key(kd: dict) -> str:
+    """Candidates with the same key share one set of input tensors (same family, specs, output, scalars)."""
+    cand = parse_source(kd["source"])
+    return repr((kd["func_name"], kd["tensor_specs"], kd["output_shape"], sorted(cand.scalars.items())))
+
+
+class SharedInputs:
+    """Seeded input tensors generated once by the parent and handed to every worker process
+    through POSIX shared memory, so that a sweep sharded over G GPUs does not pay G times for
+    the host-side random number generation (which costs more than timing a dozen candidates).
+
+    ``publish`` copies the arrays of one batch into named blocks and returns a small descriptor
+    (names, shapes, dtypes) that travels to the workers inside ``opts``; ``attach`` maps them
+    read-only as numpy arrays in the worker.  The parent keeps the blocks alive until ``close``.
+    """
+
+    def __init__(self):
+        self._blocks = []
+
+    def publish(self, tensors: dict) -> dict:
+        from multiprocessing import shared_memory
+
+        import numpy as np
+
+        desc = {}
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr)
+            raw = arr.view(np.uint8).reshape(-1)
+            shm = shared_memory.SharedMemory(create=True, size=max(1, raw.nbytes))
+            np.frombuffer(shm.buf, dtype=np.uint8, count=raw.nbytes)[:] = raw
+            self._blocks.append(shm)
+            desc[name] = {"shm": shm.name, "shape": list(arr.shape), "dtype": arr.dtype.name}
+        return desc
+
+    @staticmethod
+    def attach(desc: dict) -> tuple[dict, list]:
+        """-> (arrays by tensor name, handles to close when the arrays are no longer needed)."""
+        from multiprocessing import shared_memory
+
+        import numpy as np
+
+        arrays, handles = {}, []
+        for name, d in desc.items():
+            shm = shared_memory.SharedMemory(name=d["shm"])
+            handles.append(shm)
+            dtype = resolve_dtype(d["dtype"])
+            count = int(np.prod(d["shape"])) if d["shape"] else 1
+            arrays[name] = np.frombuffer(shm.buf, dtype=dtype, count=count).reshape(d["shape"])
+        return arrays, handles
+
+    def close(self) -> None:
+        for shm in self._blocks:
+            try:
+                shm.close()
+                shm.unlink()
+            except FileNotFoundError:
+                pass
+        self._blocks = []
+
+
 def gpu_shard_worker(items: list[dict], opts: dict, emit: Callable[[ProfileResult], None]) -> None:
     """Time every candidate of one shard on the current process's GPU 0.
 
-    Inputs are regenerated from the seed in this process (same seed -> same tensors on every
-    GPU), grouped so that candidates that share input specs share one device copy.
+    Inputs come, in this order of preference, from ``opts["inputs"]`` (arrays the caller already
+    holds), from ``opts["shared_inputs"]`` (shared-memory blocks published by the parent, keyed
+    by batch) or from the seed (same seed -> same tensors on every GPU).  Candidates that share
+    input specs share one device copy.
     """
     from autotune.runner.benchmark import DeviceBatch, benchmark_one, generate_tensors
 
@@ -89,12 +151,21 @@ def gpu_shard_worker(items: list[dict], opts: dict, emit: Callable[[ProfileResul
         cr = CompileResult(kd["kernel_name"], kd["nki_path"], "", "")
         try:
             cand = parse_source(kd["source"])
-            key = repr((kd["func_name"], kd["tensor_specs"], kd["output_shape"], sorted(cand.scalars.items())))
+            key = batch_key(kd)
             if key not in batches:
                 batches.clear()  # one batch resident at a time bounds device memory
-                kwargs = generate_tensors(kd["tensor_specs"], opts["seed"])
+                handles: list = []
+                if opts.get("inputs") is not None:
+                    kwargs = {n: opts["inputs"][n] for n in kd["tensor_specs"]}
+                elif key in (opts.get("shared_inputs") or {}):
+                    kwargs, handles = SharedInputs.attach(opts["shared_inputs"][key])
+                else:
+                    kwargs = generate_tensors(kd["tensor_specs"], opts["seed"])
                 out = OutputSpec(_OUTPUT_TENSOR_NAME, kd["output_shape"], resolve_dtype(kd["input_dtype_name"]))
                 batches[key] = DeviceBatch(kd["func_name"], kwargs, out, cand.scalars)
+                del kwargs
+                for h in handles:  # the device copy exists: the mapping can go
+                    h.close()
             result = benchmark_one(
                 batches[key], cr, cand, warmup=opts["warmup"], iters=opts["iters"],
                 collect_detailed_profile=opts["detailed"],
@@ -233,6 +304,27 @@ def run_sharded(
 
 
 # ----------------------------------------------------------------------------- pipeline
+def _publish_inputs(shared: SharedInputs, accepted: list[dict], seed: int, inputs: dict | None) -> dict:
+    """One set of input tensors per distinct batch of the accepted candidates, generated (or taken
+    from ``inputs``) once in this process and published to shared memory -> {batch key: descriptor}."""
+    from autotune.runner.benchmark import generate_tensors
+
+    published: dict[str, dict] = {}
+    for kd in accepted:
+        try:
+            key = batch_key(kd)
+        except Exception:  # noqa: BLE001 - a candidate that does not parse fails in its worker, as a row
+            continue
+        if key in published:
+            continue
+        if inputs is not None:
+            tensors = {n: inputs[n] for n in kd["tensor_specs"]}
+        else:
+            tensors = generate_tensors(kd["tensor_specs"], seed)
+        published[key] = shared.publish(tensors)
+    return published
+
+
 def _visible_devices(n_detected: int) -> list[str]:
     env = os.environ.get("CUDA_VISIBLE_DEVICES")
     if env:
@@ -291,13 +383,19 @@ def run_pipeline(
     collect_compiler_logs: bool,
     collect_detailed_profile: bool,
     n_gpus: int | None = None,
-    warmup: int = 3,
-    iters: int = 10,
+    warmup: int = 10,
+    iters: int = 50,
     deadline_s: float = DEFAULT_DEADLINE_S,
     shard: tuple[int, int] | None = None,
     retime_top: int = 0,
+    inputs: dict | None = None,
 ) -> tuple[list[ProfileResult], dict[str, str]]:
     """Validate + time every candidate; returns ``(results, compiler_logs)``.
+
+    ``inputs``: input arrays by tensor name that the caller already holds (they must be what the
+    seed and specs would give); the sweep then generates nothing.  Without it the tensors are
+    generated from the seed once, in this process, and reach the worker processes through
+    shared memory.
 
     ``retime_top`` > 0: after a sweep sharded over several GPUs by this process, the fastest
     ``retime_top`` candidates are timed again on the first GPU (see ``retime_top_k``).
@@ -349,7 +447,8 @@ def run_pipeline(
             else:
                 accepted.append(kd)
 
-        opts = {"seed": seed, "warmup": warmup, "iters": iters, "detailed": collect_detailed_profile}
+        opts = {"seed": seed, "warmup": warmup, "iters": iters, "detailed": collect_detailed_profile,
+                "inputs": inputs}
         hw_results: list[ProfileResult] = []
         if shard is not None:
             rank, world = shard
@@ -361,11 +460,17 @@ def run_pipeline(
             if n_use <= 1:
                 gpu_shard_worker(accepted, opts, hw_results.append)
             else:
-                shards = shard_round_robin(accepted, n_use)
-                devices = _visible_devices(n_use)
-                hw_results = run_sharded(shards, gpu_shard_worker, opts, devices, deadline_s)
-                if retime_top > 0:
-                    hw_results = retime_top_k(hw_results, accepted, retime_top, opts, devices[0], deadline_s)
+                shared = SharedInputs()
+                try:
+                    opts["shared_inputs"] = _publish_inputs(shared, accepted, seed, inputs)
+                    opts["inputs"] = None  # the arrays travel as shared-memory names, not through pickles
+                    shards = shard_round_robin(accepted, n_use)
+                    devices = _visible_devices(n_use)
+                    hw_results = run_sharded(shards, gpu_shard_worker, opts, devices, deadline_s)
+                    if retime_top > 0:
+                        hw_results = retime_top_k(hw_results, accepted, retime_top, opts, devices[0], deadline_s)
+                finally:
+                    shared.close()
 
         logs: dict[str, str] = {}
         if collect_compiler_logs:

@@ -8,7 +8,9 @@ as NCCL collectives over NVLink, each landing in local memory before any kernel 
 * ``replicate`` -- ``rhs`` is uploaded once (by ``src``) and broadcast, instead of one
   host-to-device copy per GPU;
 * ``gather_rows`` -- the row blocks of C are all-gathered on the device, instead of one
-  device-to-host copy per GPU followed by a host-side concatenation.
+  device-to-host copy per GPU followed by a host-side concatenation;
+* with ``chunks > 1`` the split is block-cyclic and the all-gather of one band of C overlaps the
+  multiplication of the next.
 
 The reference has no multi-device path (its benchmark loop is one device, serial:
 autotune/src/autotune/runner/driver.py:97); this is the sharding its large-M configuration needs.
@@ -24,7 +26,7 @@ from typing import Callable
 import torch
 import torch.distributed as dist
 
-from autotune import kernels
+from autotune import kernels, native
 
 
 def row_range(M: int, rank: int, world: int, align: int = 8) -> tuple[int, int]:
@@ -85,6 +87,17 @@ def gather_rows(c_block: torch.Tensor, M: int, group=None, out: torch.Tensor | N
     return out
 
 
+def cyclic_rows(M: int, rank: int, world: int, chunks: int) -> list[tuple[int, int]]:
+    """Rows of C owned by ``rank`` when the split is block-cyclic: M is cut into ``chunks`` bands of
+    ``world`` equal pieces and rank r owns piece r of every band.  The pieces of one band are one
+    contiguous range of C, which is what lets the band be all-gathered in place while the next band
+    is still being multiplied.  Needs M divisible by ``8 * world * chunks``."""
+    if chunks < 1 or M % (8 * world * chunks) != 0:
+        raise ValueError(f"M={M} must be a multiple of 8 * world * chunks = {8 * world * chunks}")
+    piece = M // (world * chunks)
+    return [((i * world + rank) * piece, (i * world + rank + 1) * piece) for i in range(chunks)]
+
+
 def matmul_lhsT_rhs_row_split(
     lhs_T_block: torch.Tensor,
     rhs: torch.Tensor,
@@ -94,20 +107,64 @@ def matmul_lhsT_rhs_row_split(
     gather: bool = True,
     out_full: torch.Tensor | None = None,
     matmul: Callable | None = None,
+    chunks: int = 1,
+    spare_ctas: int = 16,
 ) -> tuple[torch.Tensor, torch.Tensor | None]:
     """This rank's rows of ``lhs_T.T @ rhs`` and, with ``gather``, the whole of C on every rank.
 
-    ``lhs_T_block`` is ``lhs_T[:, m0:m1]`` for ``(m0, m1) = row_range(M, rank, world)`` -- a view with
-    the full row stride is fine, no copy is made -- and ``rhs`` this rank's replica (see
-    ``replicate``).  ``matmul(lhs_T_block, rhs, cfg=..., out=...)`` defaults to the tcgen05 GEMM.
+    ``chunks == 1``: ``lhs_T_block`` is ``lhs_T[:, m0:m1]`` for ``(m0, m1) = row_range(M, rank, world)``
+    -- a view with the full row stride is fine, no copy is made -- and ``rhs`` this rank's replica
+    (see ``replicate``); the all-gather runs after the kernel.
+
+    ``chunks > 1`` (needs ``gather``): the split is block-cyclic (``cyclic_rows``); ``lhs_T_block``
+    holds the columns of ``lhs_T`` for this rank's pieces, band after band.  Band i is multiplied on
+    the current stream while band i-1 is all-gathered (in place, into its contiguous range of C) on
+    a second stream, so that only the last band's exchange is not hidden.  The GEMM's grid is kept
+    ``spare_ctas`` CTAs below the machine, which leaves the collective's CTAs room to be resident
+    beside it.  Returns ``(None, out_full)`` in this mode: the rank's rows are not one block.
+
+    ``matmul(lhs_T_block, rhs, cfg=..., out=...)`` defaults to the tcgen05 GEMM.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
+    run = matmul if matmul is not None else kernels.matmul_lhsT_rhs
+    n = rhs.shape[1]
+    if chunks > 1:
+        if not gather:
+            raise ValueError("chunks > 1 is the overlapped all-gather: it needs gather=True")
+        pieces = cyclic_rows(M, rank, world, chunks)
+        piece = pieces[0][1] - pieces[0][0]
+        if lhs_T_block.shape[1] != piece * chunks:
+            raise ValueError(f"rank {rank}: lhs_T block has {lhs_T_block.shape[1]} columns, the cyclic split gives {piece * chunks}")
+        if out_full is None:
+            out_full = torch.empty((M, n), dtype=lhs_T_block.dtype, device=lhs_T_block.device)
+        use_cfg = cfg
+        if matmul is None and lhs_T_block.is_cuda and spare_ctas > 0:
+            sms = torch.cuda.get_device_properties(lhs_T_block.device).multi_processor_count
+            base = dict(cfg) if cfg is not None else native.default_cfg("matmul_lhsT_rhs", piece, n, lhs_T_block.shape[0])
+            use_cfg = dict(base, _max_ctas=max(2, sms - spare_ctas))
+        on_gpu = lhs_T_block.is_cuda
+        comm = _comm_stream(lhs_T_block.device) if on_gpu else None
+        main = torch.cuda.current_stream(lhs_T_block.device) if on_gpu else None
+        if on_gpu:
+            comm.wait_stream(main)  # out_full may still be read by work queued earlier
+        for i, (p0, p1) in enumerate(pieces):
+            band = out_full[i * world * piece:(i + 1) * world * piece]
+            run(lhs_T_block[:, i * piece:(i + 1) * piece], rhs, cfg=use_cfg, out=out_full[p0:p1])
+            if on_gpu:
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    dist.all_gather_into_tensor(band, out_full[p0:p1], group=group)
+            else:
+                dist.all_gather_into_tensor(band, out_full[p0:p1].contiguous(), group=group)
+        if on_gpu:
+            main.wait_stream(comm)
+        return None, out_full
     m0, m1 = row_range(M, rank, world)
     if lhs_T_block.shape[1] != m1 - m0:
         raise ValueError(f"rank {rank}: lhs_T block has {lhs_T_block.shape[1]} columns, row_range gives {m1 - m0}")
-    run = matmul if matmul is not None else kernels.matmul_lhsT_rhs
-    n = rhs.shape[1]
     if gather and out_full is None:
         out_full = torch.empty((M, n), dtype=lhs_T_block.dtype, device=lhs_T_block.device)
     if gather and len({b1 - b0 for b0, b1 in (row_range(M, r, world) for r in range(world))}) == 1:
@@ -121,3 +178,14 @@ def matmul_lhsT_rhs_row_split(
     if not gather:
         return c_block, None
     return c_block, gather_rows(c_block, M, group=group, out=out_full)
+
+
+_COMM_STREAMS: dict = {}
+
+
+def _comm_stream(device) -> "torch.cuda.Stream":
+    """One side stream per device for the exchange steps that overlap the kernels."""
+    key = torch.device(device).index
+    if key not in _COMM_STREAMS:
+        _COMM_STREAMS[key] = torch.cuda.Stream(device)
+    return _COMM_STREAMS[key]

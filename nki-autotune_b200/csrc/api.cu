@@ -196,6 +196,9 @@ static int make_plan(Family fam, const b200_cfg* cfg_in, long M, long N, long K,
     }
   }
   p.group_m = cfg.swizzle > 0 ? cfg.swizzle : (cfg.tile_m == 512 ? 4 : (p.cta_group == 2 || p.m_sub == 2 ? 8 : 16));
+  // prologue variant: narrow groups, so that the first wave of tiles reads few rows of x (about 1024)
+  // and can start as soon as the norm pass has covered those
+  if (prologue && cfg.swizzle == 0) p.group_m = cfg.tile_m >= 1024 ? 1 : 1024 / cfg.tile_m;
 
   const int acc_cols = p.m_sub * p.tile_n;
   const long mc = 128L * p.m_sub;
@@ -415,9 +418,14 @@ struct LaunchArgs {
 
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
-// prologue variant: [xg: M*K bf16][rinv: M fp32][grid barrier counters: 2 x u32]
+// prologue variant: [xg: M*K bf16][rinv: M fp32][counters: next row, departed CTAs, one per 128 rows]
 static size_t prologue_workspace_bytes(long M, long K) {
-  return align256(static_cast<size_t>(M) * K * 2) + align256(static_cast<size_t>(M) * sizeof(float)) + 256;
+  return align256(static_cast<size_t>(M) * K * 2) + align256(static_cast<size_t>(M) * sizeof(float)) +
+         align256((2 + static_cast<size_t>((M + 127) / 128)) * sizeof(unsigned int))
+#ifdef B200_MEASURE_HOOKS
+         + 160 * 8 * sizeof(unsigned long long)  // measurement build: per-CTA stamps behind the counters
+#endif
+      ;
 }
 
 // skinny kernel: [tile counters: one int per 256-column tile, zero between launches]
@@ -626,10 +634,14 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
     gp.gamma = static_cast<const __nv_bfloat16*>(la.gamma);
     gp.xg = la.gamma != nullptr ? reinterpret_cast<__nv_bfloat16*>(ws) : nullptr;  // no gamma: nothing to rewrite
     gp.rinv = reinterpret_cast<float*>(ws + align256(static_cast<size_t>(la.M) * la.K * 2));
-    gp.grid_sync = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(gp.rinv) +
+    gp.norm_sync = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(gp.rinv) +
                                                    align256(static_cast<size_t>(la.M) * sizeof(float)));
     gp.eps = la.eps;
     gp.inv_k = 1.0f / static_cast<float>(la.K);
+#ifdef B200_MEASURE_HOOKS
+    gp.trace = reinterpret_cast<unsigned long long*>(
+        ws + prologue_workspace_bytes(la.M, la.K) - 160 * 8 * sizeof(unsigned long long));
+#endif
   }
 
   const bool fused = (la.fam == FAM_RMSNORM) && !plan.prologue;
@@ -695,6 +707,9 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   // work units per CTA group: a CTA pair shares one tile, co-scheduled single CTAs take one each
   const long units = (plan.cta_group == 2) ? total_tiles : (total_tiles + plan.cluster - 1) / plan.cluster;
   if (groups > units) groups = units;
+  // caller's cap on the grid (b200_cfg.reserved[3], in CTAs): leaves SMs free for kernels that must
+  // run beside this one, such as a collective on another stream
+  if (cfg && cfg->reserved[3] > 0 && groups > cfg->reserved[3] / plan.cluster) groups = cfg->reserved[3] / plan.cluster;
   if (groups < 1) groups = 1;
   pr->grid = dim3(static_cast<unsigned>(groups * plan.cluster));
   if (getenv("B200_AUTOTUNE_DEBUG") != nullptr)

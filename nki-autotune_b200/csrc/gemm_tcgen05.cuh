@@ -71,7 +71,11 @@ struct GemmParams {
   const __nv_bfloat16* gamma;  // [K] or nullptr
   __nv_bfloat16* xg;           // scratch [M,K]: x * gamma, the K-major A operand of the main loop
   float* rinv;                 // scratch [M]: rsqrt(mean_k x^2 + eps)
-  unsigned int* grid_sync;     // scratch [2]: arrive / depart counters, zero between launches
+  unsigned int* norm_sync;     // scratch: [0] next row to claim, [1] CTAs that have left, [2 + i] rows of
+                               // 128-row block i that are ready; all zero between launches
+#ifdef B200_MEASURE_HOOKS
+  unsigned long long* trace;   // measurement build: 8 globaltimer stamps per CTA (NORM variant)
+#endif
   float eps, inv_k;
 };
 
@@ -143,13 +147,16 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int gro
 }
 
 // A_MODE 0: C = lhsT^T . rhs (A MN-major from lhsT[K,M]).
-// A_MODE 1 (NORM): out = (x / rms(x) * gamma) . w in one launch with a prologue: every CTA first
-//   scales its share of the rows of x by gamma into the scratch xg and stores rinv[m]; after a
-//   grid-wide barrier (all CTAs are resident: the grid never exceeds what fits the machine) the
-//   same main loop runs with A = xg (K-major) and the epilogue multiplies row m by rinv[m].
+// A_MODE 1 (NORM): out = (x / rms(x) * gamma) . w in one launch.  The epilogue warps of all CTAs
+//   first run the norm pass: rows of x scaled by gamma go to the scratch xg, rinv[m] is stored, and
+//   a counter per block of 128 rows says how many of its rows are done.  The same main loop runs
+//   with A = xg (K-major); a producer waits (bounded) only for the row blocks of the tile it is
+//   about to load, so the main loop of the first tiles overlaps the norm pass over later rows and
+//   no CTA depends on the whole grid being resident.  The epilogue multiplies row m by rinv[m].
 //   x is read once; xg costs one extra write and read of M*K*2 bytes, hidden under the tensor
 //   work.  (kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 is the two-pass form of the
-//   same maths.)
+//   same maths; its per-K-block interleaving of statistics and matmul, :307-346, is what the
+//   overlap stands for.)
 // A_MODE 2: C = lhs . rhs with lhs[M,K] K-major (matmul_lhs_rhs): the K-major operand path of
 //   the NORM variant without prologue or row scale.  The reference needs a DMA-transpose pass
 //   for this layout (kernel_library/matmul/lhs_rhs/kernel_handtuned_89.26mfu.py:226-287); the
@@ -197,6 +204,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int first_tile = static_cast<int>(blockIdx.x) / CTA_GROUP;
   const int tile_stride = static_cast<int>(gridDim.x) / CTA_GROUP;
 
+  // NORM: every warp claims its first row of the norm pass now; the answer arrives during set-up
+  [[maybe_unused]] int norm_claim = 0;
+  if constexpr (NORM) {
+    if (lane == 0 && warp >= 2) norm_claim = static_cast<int>(atomicAdd(p.norm_sync, 2u));
+  }
+#ifdef B200_MEASURE_HOOKS
+  if constexpr (NORM) {
+    if (p.trace != nullptr && threadIdx.x == 0) p.trace[blockIdx.x * 8 + 0] = global_timer_ns();  // entry
+  }
+#endif
   long long life_c0 = 0;
   unsigned long long life_n0 = 0;
   if (p.record_clocks && threadIdx.x == 0) {
@@ -234,89 +251,109 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   WaitCtx wctx{ctrl, p.status, p.timeout_cycles, 0};
 
-  if constexpr (NORM) {
-    // ---------------------------------------------------------------- prologue: xg, rinv
-    // gamma is the same for every row: it is staged once in the (still unused) operand stages of
-    // shared memory when it fits, so that the loads in flight are all x (sixteen 16-byte pieces
-    // per lane: the pass is memory-bound and only six warps per SM run it)
-    const int pieces = p.K / 8;  // 16-byte pieces per row (K is a multiple of 64)
-    const bool gamma_in_smem = p.gamma != nullptr && static_cast<uint32_t>(p.K) * 2u <= stages * (a_bytes + b_bytes);
-    const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
-    if (gamma_in_smem) {
-      for (int i = threadIdx.x; i < pieces; i += GEMM_THREADS)
-        st_shared_v4(a_base + static_cast<uint32_t>(i) * 16u, __ldg(reinterpret_cast<const uint4*>(p.gamma) + i));
-      __syncthreads();
-    }
-    const int warps_total = static_cast<int>(gridDim.x) * (GEMM_THREADS / 32);
-    for (int row = static_cast<int>(blockIdx.x) * (GEMM_THREADS / 32) + warp; row < p.M; row += warps_total) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K);
-      uint4* dst = reinterpret_cast<uint4*>(p.xg + static_cast<long long>(row) * p.K);
-      float ss = 0.0f, ss2 = 0.0f;
-      for (int i0 = lane; i0 < pieces; i0 += 512) {
-        uint4 v[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int i = i0 + u * 32;
-          v[u] = (i < pieces) ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+  // NORM: rows of x are ready for the main loop (xg written, rinv stored) in blocks of 128 rows;
+  // norm_ready() waits, bounded, until block `blk` is complete.  Every lane polls the same word
+  // (one transaction), so whichever lane is elected for the copies has made the acquire itself.
+  constexpr int NORM_BLOCK = 128;
+  auto norm_ready = [&](int blk, int tile) -> bool {
+    const unsigned want = static_cast<unsigned>(min(NORM_BLOCK, p.M - blk * NORM_BLOCK));
+    const int* word = reinterpret_cast<const int*>(p.norm_sync + 2 + blk);
+    if (static_cast<unsigned>(ld_acquire_gpu(word)) >= want) return true;
+    const long long t0 = clock64();
+    while (static_cast<unsigned>(ld_acquire_gpu(word)) < want) {
+      if (ctrl->abort_flag) return false;
+      if (clock64() - t0 > p.timeout_cycles) {
+        ctrl->abort_flag = 1;
+        if (p.status != nullptr && atomicCAS(p.status, 0, 7) == 0) {
+          p.status[1] = wctx.role;
+          p.status[2] = 600;  // rows of x not ready
+          p.status[3] = tile;
+          p.status[4] = blk;
+          p.status[5] = static_cast<int>(blockIdx.x);
         }
+        return false;
+      }
+      __nanosleep(100);
+    }
+    return true;
+  };
+  // ---------------------------------------------------------------- the norm pass over x
+  // xg = x * gamma (bf16, one rounding) and rinv[m], two rows per claim from a global counter (any
+  // CTA that runs makes progress; all warps of the grid work on the same thousand rows, so row
+  // blocks become ready in the order the tiles need them).  The four epilogue warps of every
+  // CTA do the pass: they have nothing to drain until the first tile is finished.  The producer
+  // and issuer warps start the main loop at once; a producer waits for the row blocks of its
+  // tile.  The loads of both rows of a claim are in flight together (32 x 16 bytes per lane)
+  // and share the gamma pieces.
+  [[maybe_unused]] const int norm_pieces = p.K / 8;  // 16-byte pieces per row (K is a multiple of 64)
+  auto norm_rows = [&](int row0) {  // rows row0 and row0 + 1 (if below M); row0 is even
+    const bool two = row0 + 1 < p.M;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
+    const uint4* src0 = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row0) * p.K);
+    const uint4* src1 = src0 + norm_pieces;
+    uint4* dst0 = reinterpret_cast<uint4*>(p.xg + static_cast<long long>(row0) * p.K);
+    uint4* dst1 = dst0 + norm_pieces;
+    float ss[2] = {0.0f, 0.0f}, tt[2] = {0.0f, 0.0f};
+    for (int i0 = lane; i0 < norm_pieces; i0 += 512) {
+      uint4 v[2][16], g[16];  // all loads of the claim are issued before the first store
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int i = i0 + u * 32;
-          const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      for (int u = 0; u < 16; ++u) {
+        const int i = i0 + u * 32;
+        v[0][u] = (i < norm_pieces) ? __ldg(src0 + i) : zero;
+        v[1][u] = (i < norm_pieces && two) ? __ldg(src1 + i) : zero;
+        g[u] = (i < norm_pieces && p.gamma != nullptr) ? __ldg(reinterpret_cast<const uint4*>(p.gamma) + i) : ones;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int i = i0 + u * 32;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint32_t w4[4] = {v[r][u].x, v[r][u].y, v[r][u].z, v[r][u].w};
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
             const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
-            ss = fmaf(lo, lo, ss);
-            ss2 = fmaf(hi, hi, ss2);
-          }
-          if (i < pieces && p.xg != nullptr) {  // without gamma the main loop reads x itself: nothing to write
-            const uint4 g = gamma_in_smem ? ld_shared_v4(a_base + static_cast<uint32_t>(i) * 16u)
-                                          : (p.gamma != nullptr ? __ldg(reinterpret_cast<const uint4*>(p.gamma) + i) : ones);
-            dst[i] = make_uint4(mul_bf16x2(v[u].x, g.x), mul_bf16x2(v[u].y, g.y), mul_bf16x2(v[u].z, g.z),
-                                mul_bf16x2(v[u].w, g.w));
+            ss[r] = fmaf(lo, lo, ss[r]);
+            tt[r] = fmaf(hi, hi, tt[r]);
           }
         }
+        if (i < norm_pieces && p.xg != nullptr) {  // without gamma the main loop reads x itself: nothing to write
+          dst0[i] = make_uint4(mul_bf16x2(v[0][u].x, g[u].x), mul_bf16x2(v[0][u].y, g[u].y),
+                               mul_bf16x2(v[0][u].z, g[u].z), mul_bf16x2(v[0][u].w, g[u].w));
+          if (two)
+            dst1[i] = make_uint4(mul_bf16x2(v[1][u].x, g[u].x), mul_bf16x2(v[1][u].y, g[u].y),
+                                 mul_bf16x2(v[1][u].z, g[u].z), mul_bf16x2(v[1][u].w, g[u].w));
+        }
       }
-      ss += ss2;
+    }
 #pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-      if (lane == 0) p.rinv[row] = rsqrtf(ss * p.inv_k + p.eps);
+    for (int r = 0; r < 2; ++r) {
+      ss[r] += tt[r];
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], off);
     }
-    // ---------------------------------------------------------------- grid-wide barrier (bounded)
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      atomicAdd(p.grid_sync, 1u);
-      const long long t0 = clock64();
-      bool arrived = true;
-      while (*reinterpret_cast<volatile unsigned int*>(p.grid_sync) < gridDim.x) {
-        if (clock64() - t0 > p.timeout_cycles) {
-          arrived = false;
-          break;
-        }
-        __nanosleep(200);
-      }
-      if (arrived) {
-        __threadfence();
-        // the last CTA to leave puts both counters back to zero for the next launch
-        if (atomicAdd(p.grid_sync + 1, 1u) == gridDim.x - 1) {
-          p.grid_sync[0] = 0u;
-          p.grid_sync[1] = 0u;
-          __threadfence();
-        }
-      } else {
-        ctrl->abort_flag = 1;
-        if (p.status != nullptr && atomicCAS(p.status, 0, 7) == 0) {
-          p.status[1] = 5;  // grid barrier
-          p.status[5] = static_cast<int>(blockIdx.x);
-        }
-      }
+    // publish: the rows' stores (all lanes'), then two more rows of their block (row0 is even, so
+    // a claim never straddles blocks)
+    __syncwarp();
+    if (lane == 0) {
+      p.rinv[row0] = rsqrtf(ss[0] * p.inv_k + p.eps);
+      if (two) p.rinv[row0 + 1] = rsqrtf(ss[1] * p.inv_k + p.eps);
+      __threadfence();
+      atomicAdd(p.norm_sync + 2 + row0 / NORM_BLOCK, two ? 2u : 1u);
     }
-    __syncthreads();
-    // order the other CTAs' generic-proxy stores to xg before this CTA's TMA (async proxy) loads
-    asm volatile("fence.proxy.async;" ::: "memory");
-  }
-  const bool run_roles = !NORM || ctrl->abort_flag == 0;
+  };
+  // works on claimed rows until the counter has passed M; the next claim is made before the
+  // current rows' loads, which hides its latency
+  auto norm_pass = [&]() {
+    int cur = __shfl_sync(0xffffffffu, norm_claim, 0);
+    while (cur < p.M) {
+      int nxt = 0;
+      if (lane == 0) nxt = static_cast<int>(atomicAdd(p.norm_sync, 2u));
+      norm_rows(cur);
+      cur = __shfl_sync(0xffffffffu, nxt, 0);
+    }
+  };
+  const bool run_roles = true;
 
   // ------------------------------------------------------------------ TMA producer
   if (!run_roles) {
@@ -328,6 +365,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t it = 0;
       Ring ring;
       bool ok = true;
+      [[maybe_unused]] unsigned long long norm_seen = 0;  // 128-row blocks of x already seen complete
       const int b_chunks = nc / 64, sub_chunks = nc_sub / 64, sub_jump = umma_n - nc_sub;
       for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride) {
         const int tile = unit / split_k, part = unit - tile * split_k;
@@ -336,6 +374,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
         const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc_sub;  // first UMMA's share; next at + umma_n
+        if constexpr (NORM) {
+          if (p.xg != nullptr) {  // A = xg: this CTA's rows of the tile must have been written
+            for (int blk = m_base / NORM_BLOCK; blk * NORM_BLOCK < min(m_base + MC, p.M) && ok; ++blk)
+              if (blk >= 64 || !((norm_seen >> blk) & 1ull)) {
+                ok = norm_ready(blk, tile);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok && blk < 64) norm_seen |= 1ull << blk;
+              }
+            if (!ok) break;
+            // order the other CTAs' generic-proxy stores to xg before this CTA's TMA (async proxy) loads
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it, ring.advance(stages)) {
           const uint32_t s = ring.s;
           const uint32_t ph = ring.ph;
@@ -430,6 +481,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           ok = bounded_wait<false>(wctx, smem_u32(&ctrl->full[s]), ring.ph, 300 + s, tile, kb);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+#ifdef B200_MEASURE_HOOKS
+          if constexpr (NORM) {
+            if (p.trace != nullptr && lane == 0 && unit == first_tile && kb == kb0) p.trace[blockIdx.x * 8 + 3] = global_timer_ns();  // first operands landed
+          }
+#endif
           tc_fence_after();
           uint64_t adesc = a_desc0 + s * a_step;
           uint64_t bdesc = b_desc0 + s * b_step;
@@ -462,6 +518,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (!ok) break;
         if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->acc_full[b]), 3);
         else umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[b]));
+#ifdef B200_MEASURE_HOOKS
+        if constexpr (NORM) {
+          if (p.trace != nullptr && lane == 0 && unit == first_tile) p.trace[blockIdx.x * 8 + 4] = global_timer_ns();  // first tile issued
+          if (p.trace != nullptr && lane == 0) p.trace[blockIdx.x * 8 + 6] = global_timer_ns();  // last tile issued
+        }
+#endif
       }
     }
     __syncwarp();
@@ -476,6 +538,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t sbuf = 0;
     Ring acc;
     bool ok = true;
+    [[maybe_unused]] unsigned long long norm_seen = 0;
+    if constexpr (NORM) {
+      // the epilogue warps have nothing to drain until the first tile is finished: they take the
+      // rest of the norm pass
+      norm_pass();
+#ifdef B200_MEASURE_HOOKS
+      if (p.trace != nullptr && threadIdx.x == 64) p.trace[blockIdx.x * 8 + 2] = global_timer_ns();  // norm pass done in this CTA
+#endif
+    }
     for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride, acc.advance(acc_bufs)) {
       const int tile = unit / split_k, part = unit - tile * split_k;
       int mt, nt;
@@ -484,15 +555,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int n_base = nt * tile_n;
       const int b = static_cast<int>(acc.s);
       const uint32_t aph = acc.ph;
+      [[maybe_unused]] float row_scale[M_SUB];
+      if constexpr (NORM) {
+        // rinv of this tile's rows comes from other CTAs: make sure their blocks are complete, and
+        // fetch the factors while the tile is still being accumulated
+        for (int blk = m_base / NORM_BLOCK; blk * NORM_BLOCK < min(m_base + MC, p.M) && ok; ++blk)
+          if (blk >= 64 || !((norm_seen >> blk) & 1ull)) {
+            ok = norm_ready(blk, tile);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && blk < 64) norm_seen |= 1ull << blk;
+          }
+        if (!ok) break;
+#pragma unroll
+        for (int mi = 0; mi < M_SUB; ++mi) {
+          const int row = m_base + mi * 128 + q * 32 + lane;
+          row_scale[mi] = row < p.M ? __ldcg(p.rinv + row) : 0.0f;
+        }
+      }
       ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_full[b]), aph, 500 + b, tile, -1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+#ifdef B200_MEASURE_HOOKS
+      if constexpr (NORM) {
+        if (p.trace != nullptr && threadIdx.x == 64 && unit == first_tile) p.trace[blockIdx.x * 8 + 5] = global_timer_ns();  // first tile seen by the epilogue
+      }
+#endif
       tc_fence_after();
 #pragma unroll
       for (int mi = 0; mi < M_SUB; ++mi) {
         const int row0 = m_base + mi * 128 + q * 32;  // first of this warp's 32 rows
         float scale = 1.0f;
-        if constexpr (NORM) scale = (row0 + lane < p.M) ? __ldcg(p.rinv + row0 + lane) : 0.0f;
+        if constexpr (NORM) scale = row_scale[mi];
         for (int c = 0; c < tile_n / 64; ++c) {
           // 64 accumulator columns of this lane's row -> bf16 -> one 128-byte row of the staging
           // buffer (16-byte chunk j lands at chunk j ^ (row & 7): the 128-byte swizzle the store's
@@ -563,6 +656,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
     }
     if (lane == 0) tma_store_wait_all<0>();  // staging buffers are read out and the rows written before exit
+#ifdef B200_MEASURE_HOOKS
+    if constexpr (NORM) {
+      if (p.trace != nullptr && threadIdx.x == 64) p.trace[blockIdx.x * 8 + 7] = global_timer_ns();  // epilogue done
+    }
+#endif
   }
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
@@ -580,6 +678,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<CTA_GROUP>(tmem_base, static_cast<uint32_t>(p.tmem_cols));
+  }
+  if constexpr (NORM) {
+    // the last CTA to leave puts the counters back to zero for the next launch (a CTA that gave
+    // up leaves them as they are: the scratch is undefined after a failed launch)
+    if (threadIdx.x == 0 && ctrl->abort_flag == 0) {
+      __threadfence();
+      if (atomicAdd(p.norm_sync + 1, 1u) == gridDim.x - 1) {
+        const int blocks = (p.M + NORM_BLOCK - 1) / NORM_BLOCK;
+        for (int i = 0; i < blocks + 2; ++i) p.norm_sync[i] = 0u;
+        __threadfence();
+      }
+    }
   }
   if (p.record_clocks && threadIdx.x == 0 && p.status != nullptr) {
     atomicMax(&p.status[6], static_cast<int>(clock64() - life_c0));

@@ -20,12 +20,16 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def native_lib():
-    """The built shared library; built on demand when nvcc is present, else the test fails."""
+    """The shared library, brought up to date with the sources whenever nvcc is present (the build
+    recompiles only what is stale, so this is a no-op for current objects); without nvcc the
+    existing library is used, and a missing one fails the test."""
+    import importlib.util
+    import shutil
+
     from autotune import native
 
-    if not native.LIB_PATH.exists():
-        import importlib.util
-
+    have_nvcc = shutil.which("nvcc") is not None or Path("/usr/local/cuda/bin/nvcc").is_file()
+    if have_nvcc:
         spec = importlib.util.spec_from_file_location("b200_build", PKG / "build.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)

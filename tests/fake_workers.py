@@ -29,3 +29,18 @@ def faulty(items, opts, emit):
         if kind == "hang":
             time.sleep(3600)
         emit(_row(it))
+
+
+def reads_shared_inputs(items, opts, emit):
+    """Attaches to the input tensors the parent published and reports a checksum per item."""
+    from autotune.runner.driver import SharedInputs
+
+    for it in items:
+        arrays, handles = SharedInputs.attach(opts["shared_inputs"][it["batch"]])
+        sums = {name: float(a.astype("float64").sum()) for name, a in arrays.items()}
+        shapes = {name: list(a.shape) for name, a in arrays.items()}
+        del arrays
+        for h in handles:
+            h.close()
+        emit(ProfileResult(it["kernel_name"], "[8, 8] float32",
+                           {"total_time": 0.001, "mfu_estimated_percent": 0.5, "sums": sums, "shapes": shapes}))

@@ -35,6 +35,39 @@ def test_pool_gathers_all_results_and_pins_devices():
     assert env_of["k_0.py"] == "0" and env_of["k_1.py"] == "1" and env_of["k_5.py"] == "2" and env_of["k_3.py"] == "0"
 
 
+def test_inputs_are_generated_once_and_reach_workers_through_shared_memory():
+    """The parent publishes one set of tensors per batch; workers in other processes map them and
+    see the same values (bf16 included); after close() the blocks are gone."""
+    import ml_dtypes
+    import numpy as np
+    from multiprocessing import shared_memory
+
+    from autotune.runner.benchmark import generate_tensors
+    from autotune.runner.driver import SharedInputs
+
+    specs = {"lhs_T": {"shape": [64, 48], "dtype": "bfloat16", "dist": {"kind": "normal", "scale": 0.125}},
+             "rhs": {"shape": [64, 40], "dtype": "float32"}}
+    tensors = generate_tensors(specs, 5)
+    assert tensors["lhs_T"].dtype == ml_dtypes.bfloat16
+    shared = SharedInputs()
+    try:
+        desc = shared.publish(tensors)
+        items = [{"kernel_name": f"k_{i}.py", "batch": "b0"} for i in range(4)]
+        res = run_sharded(shard_round_robin(items, 2), fake_workers.reads_shared_inputs, {"shared_inputs": {"b0": desc}},
+                          [None, None], deadline_s=30, startup_s=60)
+        assert len(res) == 4
+        for r in res:
+            assert r.profiler_summary["shapes"] == {"lhs_T": [64, 48], "rhs": [64, 40]}
+            for name, arr in tensors.items():
+                assert r.profiler_summary["sums"][name] == float(arr.astype(np.float64).sum())
+        names = [d["shm"] for d in desc.values()]
+    finally:
+        shared.close()
+    for n in names:
+        with pytest.raises(FileNotFoundError):
+            shared_memory.SharedMemory(name=n)
+
+
 def test_top_k_is_timed_again_on_one_device():
     from autotune.runner.driver import retime_top_k
 
@@ -171,6 +204,18 @@ ROW_SPLIT_SCRIPT = textwrap.dedent(
                           bool(torch.allclose(full, want)), list(full.shape)]
         only, none = matmul_lhsT_rhs_row_split(lhs_T[:, m0:m1], rhs, M, matmul=host_matmul, gather=False)
         assert none is None and torch.allclose(only, want[m0:m1])
+    # block-cyclic split: band i of C is gathered while band i+1 is multiplied
+    from autotune.sharded import cyclic_rows
+    M, K, N, chunks = 48 * world, 24, 16, 2
+    g = torch.Generator().manual_seed(6)
+    lhs_T = torch.randn(K, M, generator=g)
+    rhs = torch.randn(K, N, generator=g)
+    pieces = cyclic_rows(M, rank, world, chunks)
+    mine = torch.cat([lhs_T[:, p0:p1] for p0, p1 in pieces], dim=1)
+    none, full = matmul_lhsT_rhs_row_split(mine, rhs, M, matmul=host_matmul, chunks=chunks)
+    result["cyclic"] = [none is None, bool(torch.allclose(full, lhs_T.T @ rhs)), list(full.shape) == [M, N],
+                        sorted(p for r in range(world) for p in cyclic_rows(M, r, world, chunks)) ==
+                        [(i * M // (world * chunks), (i + 1) * M // (world * chunks)) for i in range(world * chunks)]]
     oks = [None] * world
     dist.all_gather_object(oks, result)
     if rank == 0:
@@ -195,3 +240,4 @@ def test_row_split_replicates_and_gathers_gloo(tmp_path, world, port):
     for res in per_rank:
         assert res["64"][:3] == [True, True, True] and res["64"][3] == [64, 16]
         assert res["1000"][:3] == [True, True, True] and res["1000"][3] == [1000, 16]
+        assert res["cyclic"] == [True, True, True, True]

@@ -168,6 +168,20 @@ def test_linearity_and_determinism_full_size(K):
     assert float((got - ref).abs().max() / ref.abs().max()) < 2e-2
 
 
+def test_host_pipeline_keeps_every_step_apart(K):
+    """The host-buffer pipeline (pinned staging, uploads / kernels / downloads overlapped over two
+    buffer sets): five different operand pairs in a row, each result against the CPU oracle."""
+    from autotune.pipeline import matmul_lhsT_rhs_pipelined
+
+    k, m, n = 512, 384, 640
+    pairs = [O.generate_inputs(40 + i, [("lhs_T", (k, m), N_(k)), ("rhs", (k, n), N_(k))], bf16=True) for i in range(5)]
+    outs = matmul_lhsT_rhs_pipelined([p["lhs_T"].astype(BF) for p in pairs], [p["rhs"].astype(BF) for p in pairs],
+                                     cfg=cfg(128, 128, 64, 3))
+    assert len(outs) == 5
+    for p, got in zip(pairs, outs):
+        assert O.max_abs_rel_err(got.astype(np.float32), O.matmul_lhsT_rhs(p["lhs_T"], p["rhs"])) <= TOL_BF16
+
+
 # ---- matmul_lhs_rhs (K-major lhs) --------------------------------------------------------------
 @pytest.mark.parametrize("k,m,n", [(64, 128, 64), (512, 256, 384), (520, 1000, 1016), (2048, 2048, 2048), (72, 136, 200)])
 @pytest.mark.parametrize("c", [cfg(128, 128, 64, 4), cfg(128, 256, 128, 2), cfg(256, 256, 64, 4, cm=2), cfg(256, 128, 64, 3), None],

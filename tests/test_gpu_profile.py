@@ -89,3 +89,30 @@ def test_bad_candidate_is_a_failure_row_not_an_exception(native_lib):
                                       {"lhs_T": ((256, 256), "bfloat16"), "rhs": ((256, 256), "bfloat16")})}
     out = profile(jobs, "", 0, "b200", False)
     assert len(out.failures) == 2 and not out.successes
+
+
+def test_candidate_whose_wait_runs_out_does_not_poison_the_next_one(native_lib):
+    """A candidate that ends with a device-side wait expiry leaves its scratch (row counters of the
+    fused kernel's norm pass) undefined.  The sweep must drop that scratch: the next candidate of
+    the same batch gets a fresh, zeroed buffer, succeeds, and leaves its counters at zero."""
+    import torch
+
+    from autotune import kernels
+    from autotune.runner.api import profile
+    from autotune.runner.candidate import Candidate, jobs_from_candidates
+
+    m, k, n = 512, 1024, 768
+    specs = {"x": ((m, k), "bfloat16"), "gamma": ((k,), "bfloat16", {"kind": "uniform", "low": 0.5, "high": 1.5}),
+             "weight": ((k, n), "bfloat16", {"kind": "normal", "scale": k ** -0.5})}
+    base = dict(tile_m=128, tile_n=128, tile_k=64, stages=3, norm_mode=2)
+    cands = [Candidate("rmsnorm_matmul", dict(base, _debug_skip_producer=1, _wait_limit_us=2000), {"eps": 1e-6}),
+             Candidate("rmsnorm_matmul", dict(base), {"eps": 1e-6})]
+    kernels.reset_workspaces()
+    out = profile(jobs_from_candidates(cands, (m, n), specs), "", 7, "b200", False, warmup=1, iters=3, n_gpus=1)
+    assert len(out.failures) == 1 and "wait expired" in out.failures[0].hardware_output
+    assert len(out.successes) == 1 and out.successes[0].kernel_name.endswith("_1.py")
+    torch.cuda.synchronize()
+    bufs = [b for key, b in kernels._WORKSPACES.items() if key[1] == "prologue"]
+    assert len(bufs) == 1
+    counters = bufs[0][-256:]  # next row to claim, departed CTAs, rows ready per 128-row block
+    assert int((counters != 0).sum()) == 0

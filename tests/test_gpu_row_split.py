@@ -1,4 +1,5 @@
-"""Large-M row split over two GPUs: NCCL replication of rhs, local tcgen05 GEMMs, device all-gather.
+"""Large-M row split over two GPUs: NCCL replication of rhs, local tcgen05 GEMMs, device all-gather;
+every rank compares its own block and its gathered copy of C with the CPU oracle.
 
 Needs two GPUs; skipped on a one-GPU box.  The ranks run as child processes under torchrun."""
 
@@ -17,10 +18,12 @@ pytestmark = pytest.mark.gpu
 SCRIPT = textwrap.dedent(
     """
     import sys, json, os
-    sys.path.insert(0, {pkg!r})
+    sys.path.insert(0, {pkg!r}); sys.path.insert(0, {repo!r})
+    import ml_dtypes, numpy as np
     import torch, torch.distributed as dist
     from autotune import kernels
     from autotune.sharded import row_range, replicate, matmul_lhsT_rhs_row_split
+    from oracle import oracle as O
 
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -28,17 +31,19 @@ SCRIPT = textwrap.dedent(
     rank, world = dist.get_rank(), dist.get_world_size()
     res = {{}}
     for M, K, N in ((4096, 512, 384), (1000, 264, 136)):   # equal blocks, ragged blocks
-        g = torch.Generator(device="cuda").manual_seed(11)     # same seed: every rank can build the answer
-        lhs_T = (torch.randn(K, M, device="cuda", generator=g) * K ** -0.5).bfloat16()
-        rhs_src = (torch.randn(K, N, device="cuda", generator=g)).bfloat16()
+        # same seed on every rank: every rank can build the answer with the CPU oracle
+        s = {{"kind": "normal", "scale": K ** -0.5}}
+        t = O.generate_inputs(11, [("lhs_T", (K, M), s), ("rhs", (K, N), s)], bf16=True)
+        want = O.matmul_lhsT_rhs(t["lhs_T"], t["rhs"])
+        lhs_T = kernels.to_device(t["lhs_T"].astype(ml_dtypes.bfloat16))
+        rhs_src = kernels.to_device(t["rhs"].astype(ml_dtypes.bfloat16))
         rhs = replicate(rhs_src if rank == 0 else None, (K, N), torch.bfloat16, "cuda", src=0)
         m0, m1 = row_range(M, rank, world)
-        status = kernels.new_status()
         block, full = matmul_lhsT_rhs_row_split(lhs_T[:, m0:m1], rhs, M)
         torch.cuda.synchronize()
-        want = lhs_T.float().T @ rhs_src.float()
-        err = ((full.float() - want).abs() / (want.abs() + want.pow(2).mean().sqrt())).max().item()
-        res[str(M)] = [bool(torch.equal(rhs, rhs_src)), err, list(full.shape)]
+        err = O.max_abs_rel_err(kernels.to_host(full).astype(np.float32), want)
+        err_block = O.max_abs_rel_err(kernels.to_host(block).astype(np.float32), want[m0:m1])
+        res[str(M)] = [bool(torch.equal(rhs, rhs_src)), max(err, err_block), list(full.shape)]
     out = [None] * world
     dist.all_gather_object(out, res)
     if rank == 0:
@@ -54,7 +59,7 @@ def test_row_split_two_gpus_nccl(native_lib, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "row_split_gpu.py"
-    script.write_text(SCRIPT.format(pkg=str(PKG)))
+    script.write_text(SCRIPT.format(pkg=str(PKG), repo=str(PKG.parent)))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", "29671", str(script)]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ))
