@@ -983,3 +983,11 @@ extern "C" int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, con
   if (rc) return rc;
   return launch(pr, stream);
 }
+
+#ifdef B200_MEASURE_HOOKS
+// measurement build only: copies the GEMM kernels' boundary stamps (g_gemm_trace) to the host
+extern "C" int b200_debug_gemm_trace(long long* host, size_t count) {
+  if (count > 160 * 16) count = 160 * 16;
+  return check_cuda(cudaMemcpyFromSymbol(host, b200::g_gemm_trace, count * sizeof(long long)), "trace copy");
+}
+#endif

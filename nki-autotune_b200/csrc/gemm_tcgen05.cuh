@@ -9,8 +9,10 @@
 //   warp 0      TMA producer   : waits empty[s], arms full[s], issues the tile loads of stage s
 //   warp 1      UMMA issuer    : waits full[s], issues tile_k/16 UMMAs per accumulator block, commits
 //                                to empty[s]; after the last k-block commits acc_full[b]
-//   warps 2-5   epilogue       : wait acc_full[b], tcgen05.ld, bf16 into swizzled staging buffers,
-//                                bulk tensor stores, arrive acc_empty[b]
+//   warps 2-9   epilogue       : wait acc_full[b], tcgen05.ld, bf16 into swizzled staging buffers,
+//                                bulk tensor stores, arrive acc_empty[b]; two warps per lane quadrant
+//                                take alternate 64-column chunks, so a 512-column accumulator (which
+//                                cannot be double-buffered) is drained in half the time
 // Warps 0 and 1 run their loops with all lanes converged and elect one lane per instruction.
 // Work units are (tile, part of the K range); without split-K a unit is a whole tile.
 //
@@ -28,11 +30,12 @@
 namespace b200 {
 
 constexpr int MAX_STAGES = 12;
-constexpr int GEMM_THREADS = 192;
-// epilogue staging in shared memory: per epilogue warp two buffers of 32 rows x 64 bf16 columns
-// (128-byte rows, 128-byte swizzle), written by the warp and read by its TMA stores
+constexpr int EPI_WARPS = 8;  // two per tensor-memory lane quadrant; they share a tile's 64-column chunks
+constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
+// epilogue staging in shared memory: per epilogue warp one buffer of 32 rows x 64 bf16 columns
+// (128-byte rows, 128-byte swizzle), written by the warp and read by its TMA store
 constexpr int EPI_BUF_BYTES = 32 * 128;
-constexpr int EPI_STAGE_BYTES = 4 * 2 * EPI_BUF_BYTES;
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_BUF_BYTES;
 
 // test hook (b200_cfg.reserved[0]): the producer issues nothing, so the consumers' bounded waits
 // run out -- how the tests exercise the give-up path without faulting anything
@@ -45,6 +48,14 @@ constexpr int DEBUG_SKIP_PRODUCER = 1;
 constexpr int DEBUG_NO_RELOAD = 2;
 constexpr int DEBUG_NO_MMA = 3;
 constexpr int DEBUG_NO_TRANSFORM = 4;
+#endif
+
+#ifdef B200_MEASURE_HOOKS
+// measurement build: clock64 stamps around the boundary between a CTA's third and fourth tile
+// ([cta][0] tile start seen by the issuer, [1] its last UMMA and commit issued, [2] next tile's start;
+// [3]/[6] accumulator seen full by an epilogue warp of either half, [4]/[7] its last tensor-memory
+// load done, [5]/[8] its arrival on acc_empty; [9] issuer's first operands of the next tile seen)
+__device__ long long g_gemm_trace[160 * 16];
 #endif
 
 struct GemmParams {
@@ -207,7 +218,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   // NORM: every warp claims its first row of the norm pass now; the answer arrives during set-up
   [[maybe_unused]] int norm_claim = 0;
   if constexpr (NORM) {
-    if (lane == 0 && warp >= 2) norm_claim = static_cast<int>(atomicAdd(p.norm_sync, 2u));
+    if (lane == 0 && warp >= 2) norm_claim = static_cast<int>(atomicAdd(p.norm_sync, 1u));
   }
 #ifdef B200_MEASURE_HOOKS
   if constexpr (NORM) {
@@ -232,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[b]), 4 * CTA_GROUP);
+      mbar_init(smem_u32(&ctrl->acc_empty[b]), EPI_WARPS * CTA_GROUP);
     }
     fence_mbar_init();
   }
@@ -278,78 +289,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     return true;
   };
   // ---------------------------------------------------------------- the norm pass over x
-  // xg = x * gamma (bf16, one rounding) and rinv[m], two rows per claim from a global counter (any
+  // xg = x * gamma (bf16, one rounding) and rinv[m], one row per claim from a global counter (any
   // CTA that runs makes progress; all warps of the grid work on the same thousand rows, so row
-  // blocks become ready in the order the tiles need them).  The four epilogue warps of every
+  // blocks become ready in the order the tiles need them).  The eight epilogue warps of every
   // CTA do the pass: they have nothing to drain until the first tile is finished.  The producer
   // and issuer warps start the main loop at once; a producer waits for the row blocks of its
-  // tile.  The loads of both rows of a claim are in flight together (32 x 16 bytes per lane)
-  // and share the gamma pieces.
+  // tile.  All loads of a row (x and gamma, 32 x 16 bytes per lane) are issued before the first
+  // store, so nothing serialises them.
   [[maybe_unused]] const int norm_pieces = p.K / 8;  // 16-byte pieces per row (K is a multiple of 64)
-  auto norm_rows = [&](int row0) {  // rows row0 and row0 + 1 (if below M); row0 is even
-    const bool two = row0 + 1 < p.M;
+  auto norm_row = [&](int row) {
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
-    const uint4* src0 = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row0) * p.K);
-    const uint4* src1 = src0 + norm_pieces;
-    uint4* dst0 = reinterpret_cast<uint4*>(p.xg + static_cast<long long>(row0) * p.K);
-    uint4* dst1 = dst0 + norm_pieces;
-    float ss[2] = {0.0f, 0.0f}, tt[2] = {0.0f, 0.0f};
+    const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K);
+    uint4* dst = reinterpret_cast<uint4*>(p.xg + static_cast<long long>(row) * p.K);
+    float ss = 0.0f, tt = 0.0f;
     for (int i0 = lane; i0 < norm_pieces; i0 += 512) {
-      uint4 v[2][16], g[16];  // all loads of the claim are issued before the first store
+      uint4 v[16], g[16];
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
         const int i = i0 + u * 32;
-        v[0][u] = (i < norm_pieces) ? __ldg(src0 + i) : zero;
-        v[1][u] = (i < norm_pieces && two) ? __ldg(src1 + i) : zero;
+        v[u] = (i < norm_pieces) ? __ldg(src + i) : zero;
         g[u] = (i < norm_pieces && p.gamma != nullptr) ? __ldg(reinterpret_cast<const uint4*>(p.gamma) + i) : ones;
       }
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
         const int i = i0 + u * 32;
+        const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const uint32_t w4[4] = {v[r][u].x, v[r][u].y, v[r][u].z, v[r][u].w};
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
-            ss[r] = fmaf(lo, lo, ss[r]);
-            tt[r] = fmaf(hi, hi, tt[r]);
-          }
+        for (int w = 0; w < 4; ++w) {
+          const float lo = __uint_as_float(w4[w] << 16), hi = __uint_as_float(w4[w] & 0xffff0000u);
+          ss = fmaf(lo, lo, ss);
+          tt = fmaf(hi, hi, tt);
         }
-        if (i < norm_pieces && p.xg != nullptr) {  // without gamma the main loop reads x itself: nothing to write
-          dst0[i] = make_uint4(mul_bf16x2(v[0][u].x, g[u].x), mul_bf16x2(v[0][u].y, g[u].y),
-                               mul_bf16x2(v[0][u].z, g[u].z), mul_bf16x2(v[0][u].w, g[u].w));
-          if (two)
-            dst1[i] = make_uint4(mul_bf16x2(v[1][u].x, g[u].x), mul_bf16x2(v[1][u].y, g[u].y),
-                                 mul_bf16x2(v[1][u].z, g[u].z), mul_bf16x2(v[1][u].w, g[u].w));
-        }
+        if (i < norm_pieces && p.xg != nullptr)  // without gamma the main loop reads x itself: nothing to write
+          dst[i] = make_uint4(mul_bf16x2(v[u].x, g[u].x), mul_bf16x2(v[u].y, g[u].y), mul_bf16x2(v[u].z, g[u].z),
+                              mul_bf16x2(v[u].w, g[u].w));
       }
     }
+    ss += tt;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      ss[r] += tt[r];
-#pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], off);
-    }
-    // publish: the rows' stores (all lanes'), then two more rows of their block (row0 is even, so
-    // a claim never straddles blocks)
+    for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    // publish: the row's stores (all lanes'), then one more row of its block
     __syncwarp();
     if (lane == 0) {
-      p.rinv[row0] = rsqrtf(ss[0] * p.inv_k + p.eps);
-      if (two) p.rinv[row0 + 1] = rsqrtf(ss[1] * p.inv_k + p.eps);
+      p.rinv[row] = rsqrtf(ss * p.inv_k + p.eps);
       __threadfence();
-      atomicAdd(p.norm_sync + 2 + row0 / NORM_BLOCK, two ? 2u : 1u);
+      atomicAdd(p.norm_sync + 2 + row / NORM_BLOCK, 1u);
     }
   };
   // works on claimed rows until the counter has passed M; the next claim is made before the
-  // current rows' loads, which hides its latency
+  // current row's loads, which hides its latency
   auto norm_pass = [&]() {
     int cur = __shfl_sync(0xffffffffu, norm_claim, 0);
     while (cur < p.M) {
       int nxt = 0;
-      if (lane == 0) nxt = static_cast<int>(atomicAdd(p.norm_sync, 2u));
-      norm_rows(cur);
+      if (lane == 0) nxt = static_cast<int>(atomicAdd(p.norm_sync, 1u));
+      norm_row(cur);
       cur = __shfl_sync(0xffffffffu, nxt, 0);
     }
   };
@@ -474,6 +469,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_empty[b]), acc.ph ^ 1u, 200 + b, tile, -1);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+#ifdef B200_MEASURE_HOOKS
+        if (lane == 0 && unit == first_tile + 2 * tile_stride) g_gemm_trace[blockIdx.x * 16 + 0] = clock64();
+        if (lane == 0 && unit == first_tile + 3 * tile_stride) g_gemm_trace[blockIdx.x * 16 + 2] = clock64();
+#endif
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * static_cast<uint32_t>(acc_cols);
         for (int kb = kb0; kb < kb1; ++kb, ring.advance(stages)) {
@@ -485,6 +484,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           if constexpr (NORM) {
             if (p.trace != nullptr && lane == 0 && unit == first_tile && kb == kb0) p.trace[blockIdx.x * 8 + 3] = global_timer_ns();  // first operands landed
           }
+          if (lane == 0 && unit == first_tile + 3 * tile_stride && kb == kb0) g_gemm_trace[blockIdx.x * 16 + 9] = clock64();
 #endif
           tc_fence_after();
           uint64_t adesc = a_desc0 + s * a_step;
@@ -519,6 +519,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->acc_full[b]), 3);
         else umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[b]));
 #ifdef B200_MEASURE_HOOKS
+        if (lane == 0 && unit == first_tile + 2 * tile_stride) g_gemm_trace[blockIdx.x * 16 + 1] = clock64();
         if constexpr (NORM) {
           if (p.trace != nullptr && lane == 0 && unit == first_tile) p.trace[blockIdx.x * 8 + 4] = global_timer_ns();  // first tile issued
           if (p.trace != nullptr && lane == 0) p.trace[blockIdx.x * 8 + 6] = global_timer_ns();  // last tile issued
@@ -529,13 +530,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
     __syncwarp();
   }
   // ------------------------------------------------------------------ epilogue
-  else if (warp < 6) {
+  else if (warp < 2 + EPI_WARPS) {
     wctx.role = ROLE_EPILOGUE;
-    const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+    const int q = warp & 3;          // tensor-memory lane quadrant this warp may read
+    const int eg = (warp - 2) >> 2;  // which of the quadrant's two warps: it takes chunks eg, eg + 2, ...
     const uint32_t acc_empty_leader =
         PAIR ? map_to_cta(smem_u32(&ctrl->acc_empty[0]), 0) : smem_u32(&ctrl->acc_empty[0]);
-    const uint32_t stage_base = out_stage_base + static_cast<uint32_t>(q) * (2 * EPI_BUF_BYTES);
-    uint32_t sbuf = 0;
+    const uint32_t buf = out_stage_base + static_cast<uint32_t>(warp - 2) * EPI_BUF_BYTES;
     Ring acc;
     bool ok = true;
     [[maybe_unused]] unsigned long long norm_seen = 0;
@@ -576,36 +577,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
 #ifdef B200_MEASURE_HOOKS
+      const bool tr = lane == 0 && (warp == 2 || warp == 6) && unit == first_tile + 2 * tile_stride;
+      const int tr0 = blockIdx.x * 16 + (warp == 2 ? 3 : 6);
+      if (tr) g_gemm_trace[tr0] = clock64();
       if constexpr (NORM) {
         if (p.trace != nullptr && threadIdx.x == 64 && unit == first_tile) p.trace[blockIdx.x * 8 + 5] = global_timer_ns();  // first tile seen by the epilogue
       }
 #endif
       tc_fence_after();
+      auto release_accumulator = [&]() {
+        // every tensor-memory load of this warp has completed (tcgen05.wait::ld): the issuer may
+        // overwrite the accumulator.  No data in memory is handed over with this arrival, so the
+        // remote form needs no release fence (which costs about 2000 cycles here).
+        tc_fence_before();
+        __syncwarp();
+#ifdef B200_MEASURE_HOOKS
+        if (tr) g_gemm_trace[tr0 + 1] = clock64();
+#endif
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster_relaxed(acc_empty_leader + b * 8);
+          else mbar_arrive(acc_empty_leader + b * 8);
+        }
+#ifdef B200_MEASURE_HOOKS
+        if (tr) g_gemm_trace[tr0 + 2] = clock64();
+#endif
+      };
+      if (split_k > 1) {
+        // split-K: this unit's fp32 partial goes to its part's array in the scratch (rows
+        // part * part_rows + ...), 32 columns = one 128-byte staging row at a time; a second
+        // kernel sums the parts.  Same staging buffer and swizzle as the bf16 path.
 #pragma unroll
-      for (int mi = 0; mi < M_SUB; ++mi) {
-        const int row0 = m_base + mi * 128 + q * 32;  // first of this warp's 32 rows
-        float scale = 1.0f;
-        if constexpr (NORM) scale = row_scale[mi];
-        for (int c = 0; c < tile_n / 64; ++c) {
-          // 64 accumulator columns of this lane's row -> bf16 -> one 128-byte row of the staging
-          // buffer (16-byte chunk j lands at chunk j ^ (row & 7): the 128-byte swizzle the store's
-          // tensor map undoes, and conflict-free for the warp's 16-byte shared stores)
-          uint32_t r0[32], r1[32];
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                 static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 64);
-          tmem_ld_32x32b_x32(taddr, r0);
-          tmem_ld_32x32b_x32(taddr + 32u, r1);
-          tmem_ld_wait();
-          const int col0 = n_base + c * 64;
-          if (split_k > 1) {
-            // split-K: this unit's fp32 partial goes to its part's array in the scratch (rows
-            // part * part_rows + ...), 32 columns = one 128-byte staging row at a time; a second
-            // kernel sums the parts.  Same staging buffers and swizzle as the bf16 path.
+        for (int mi = 0; mi < M_SUB; ++mi) {
+          const int row0 = m_base + mi * 128 + q * 32;  // first of this warp's 32 rows
+          for (int c = eg; c < tile_n / 64; c += EPI_WARPS / 4) {
+            uint32_t r0[32], r1[32];
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                   static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 64);
+            tmem_ld_32x32b_x32(taddr, r0);
+            tmem_ld_32x32b_x32(taddr + 32u, r1);
+            tmem_ld_wait();
+            const int col0 = n_base + c * 64;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               if (row0 < p.M && col0 + 32 * h < p.N) {
-                const uint32_t buf = stage_base + sbuf * EPI_BUF_BYTES;
-                if (lane == 0) tma_store_wait_read<1>();
+                if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
                 const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane & 7);
@@ -620,39 +635,71 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
                   tma_store_2d(&tm_out, buf, col0 + 32 * h, part * p.part_rows + row0);
                   tma_store_commit();
                 }
-                sbuf ^= 1u;
               }
             }
-          } else if (row0 < p.M && col0 < p.N) {  // warp-uniform; rows / columns past the edge are clipped by the store
-            const uint32_t buf = stage_base + sbuf * EPI_BUF_BYTES;
-            if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer has drained it
-            __syncwarp();
-            const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
-            const uint32_t sw = static_cast<uint32_t>(lane & 7);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t* r = (j < 4) ? (r0 + j * 8) : (r1 + (j - 4) * 8);
-              st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4),
-                           pack_bf16x2(__uint_as_float(r[0]) * scale, __uint_as_float(r[1]) * scale),
-                           pack_bf16x2(__uint_as_float(r[2]) * scale, __uint_as_float(r[3]) * scale),
-                           pack_bf16x2(__uint_as_float(r[4]) * scale, __uint_as_float(r[5]) * scale),
-                           pack_bf16x2(__uint_as_float(r[6]) * scale, __uint_as_float(r[7]) * scale));
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tm_out, buf, col0, row0);
-              tma_store_commit();
-            }
-            sbuf ^= 1u;
           }
         }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (PAIR) mbar_arrive_cluster(acc_empty_leader + b * 8);
-        else mbar_arrive(acc_empty_leader + b * 8);
+        release_accumulator();
+      } else {
+        // Phase 1: all of this warp's chunks (at most four: two per 128-row block, or four of a
+        // 512-column tile) go from tensor memory to registers as packed bf16, 64 accumulator
+        // columns of this lane's row at a time, and the accumulator is released -- the issuer
+        // starts the next tile while phase 2 runs.  Phase 2: chunk by chunk, one 128-byte row per
+        // lane into the staging buffer (16-byte piece j lands at piece j ^ (row & 7): the
+        // 128-byte swizzle the store's tensor map undoes, conflict-free for the warp's 16-byte
+        // shared stores), then one bulk tensor store; rows / columns past the edge are clipped.
+        constexpr int SLOTS = 4, PER_MI = SLOTS / M_SUB;
+        uint32_t packed[SLOTS][32];
+#pragma unroll
+        for (int mi = 0; mi < M_SUB; ++mi) {
+          float scale = 1.0f;
+          if constexpr (NORM) scale = row_scale[mi];
+#pragma unroll
+          for (int ci = 0; ci < PER_MI; ++ci) {
+            const int c = eg + ci * (EPI_WARPS / 4);
+            if (c < tile_n / 64) {
+              const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                     static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 64);
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {  // 32 columns at a time keeps the register peak below the cap
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + 32u * h, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  packed[mi * PER_MI + ci][16 * h + j] =
+                      pack_bf16x2(__uint_as_float(r[2 * j]) * scale, __uint_as_float(r[2 * j + 1]) * scale);
+              }
+            }
+          }
+        }
+        release_accumulator();
+#pragma unroll
+        for (int mi = 0; mi < M_SUB; ++mi) {
+          const int row0 = m_base + mi * 128 + q * 32;  // first of this warp's 32 rows
+#pragma unroll
+          for (int ci = 0; ci < PER_MI; ++ci) {
+            const int c = eg + ci * (EPI_WARPS / 4);
+            const int col0 = n_base + c * 64;
+            if (c < tile_n / 64 && row0 < p.M && col0 < p.N) {  // warp-uniform
+              if (lane == 0) tma_store_wait_read<0>();  // the store that last read the buffer has drained it
+              __syncwarp();
+              const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+              const uint32_t sw = static_cast<uint32_t>(lane & 7);
+              const uint32_t* pk = packed[mi * PER_MI + ci];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2],
+                             pk[4 * j + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tm_out, buf, col0, row0);
+                tma_store_commit();
+              }
+            }
+          }
+        }
       }
     }
     if (lane == 0) tma_store_wait_all<0>();  // staging buffers are read out and the rows written before exit
