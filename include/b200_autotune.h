@@ -91,6 +91,16 @@ int b200_device_count(int* count);
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
                    long* smem_bytes, int* tmem_cols);
 
+/* Describes, without launching anything, what a launch of this candidate at this shape is: one
+ * JSON object in out[out_bytes] (NUL-terminated) with the kernel variant, grid, cluster, threads,
+ * shared-memory bytes, tensor-memory columns, tiles / CTA groups / waves of the persistent schedule,
+ * the UMMA-issue-bound SM cycles of the busiest CTA group, and the compiled kernel's registers and
+ * local-memory bytes (null without a device).  This is what a detailed profile stores per candidate
+ * in place of the reference's per-instruction profile JSON and NEFF
+ * (autotune/src/autotune/runner/benchmark.py:81-84, 90-113; output.py:176-199). */
+int b200_describe_launch(const char* family, const b200_cfg* cfg, long M, long N, long K,
+                         char* out, size_t out_bytes);
+
 /* The candidate the library uses when an entry point is called with cfg == NULL, for this family
  * and shape (the fused family: norm_mode 0 and the tile of the variant that runs without scratch).
  * The reference has no counterpart: its hand kernels carry fixed tile constants

@@ -84,6 +84,7 @@ SIGNATURES = {
         C.c_int,
         [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long, C.POINTER(C.c_long), C.POINTER(C.c_int)],
     ),
+    "b200_describe_launch": (C.c_int, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long, C.c_char_p, C.c_size_t]),
     "b200_default_cfg": (C.c_int, [C.c_char_p, C.c_long, C.c_long, C.c_long, C.POINTER(Cfg)]),
     "b200_workspace_bytes": (C.c_size_t, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long]),
     "b200_matmul_lhsT_rhs": (
@@ -168,6 +169,17 @@ def cfg_check(family: str, cfg: dict | None, M: int = 0, N: int = 0, K: int = 0)
     status = lib.b200_cfg_check(family.encode(), C.byref(c) if c is not None else None, M, N, K,
                                 C.byref(smem), C.byref(tmem))
     return status, (last_error() if status else ""), smem.value, tmem.value
+
+
+def describe_launch(family: str, cfg: dict | None, M: int, N: int, K: int) -> dict:
+    """The launch plan of a candidate at a shape (kernel variant, grid, shared / tensor memory, waves,
+    UMMA-bound cycles, registers); nothing is launched."""
+    import json
+
+    buf = C.create_string_buffer(2048)
+    c = Cfg.from_dict(cfg)
+    check(load().b200_describe_launch(family.encode(), C.byref(c) if c is not None else None, M, N, K, buf, len(buf)))
+    return json.loads(buf.value.decode())
 
 
 def device_count() -> int:

@@ -83,7 +83,24 @@ def profile(
 
     if cache_dir:
         write_compiler_logs(cache_dir, compiler_logs)
-        write_results_json(cache_dir, len(kernels), results, elapsed_s)
+        write_results_json(cache_dir, len(kernels), results, elapsed_s, _run_metadata(results, seed, warmup, iters, n_gpus, shard))
         logger.info("Cache saved to %s", cache_dir)
 
     return ProfileOutput(results=results, compiler_logs=compiler_logs, elapsed_s=elapsed_s, cache_dir=cache_dir)
+
+
+def _run_metadata(results, seed: int, warmup: int, iters: int, n_gpus, shard) -> dict:
+    """What ``results.json`` needs beyond the reference's two metadata keys to be read on its own."""
+    from autotune.peaks import load_peaks
+    from autotune.runner.benchmark import TOL_BF16, TOL_FP32
+
+    devices = sorted({(r.profiler_summary or {}).get("device") for r in results} - {None})
+    indices = sorted({(r.profiler_summary or {}).get("device_index") for r in results} - {None})
+    return {
+        "gpu_name": devices[0] if devices else None,
+        "n_gpus": (shard[1] if shard else None) or n_gpus or max(1, len(indices)),
+        "peaks": load_peaks(),
+        "seed": seed,
+        "tolerance": {"bf16_max_abs_rel_err": TOL_BF16, "fp32_max_abs_rel_err": TOL_FP32},
+        "timing": {"warmup": warmup, "iters": iters, "statistic": "median"},
+    }

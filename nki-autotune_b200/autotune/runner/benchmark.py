@@ -133,6 +133,7 @@ def benchmark_one(
     hardware_output = f"{list(out.shape)} {out.dtype}"
     summary: dict[str, Any] | None = None
     detailed: dict[str, Any] | None = None
+    neff_b64 = ntff_b64 = None
     try:
         batch.out.zero_()
         batch.status.zero_()
@@ -172,8 +173,8 @@ def benchmark_one(
             "device": torch.cuda.get_device_name(torch.cuda.current_device()),
             "device_index": torch.cuda.current_device(),
         }
-        if collect_detailed_profile:
-            detailed = {"launches_ms": [float(x) for x in ms], "warmup": warmup, "iters": iters}
+        if collect_detailed_profile and not batch.is_fp32:
+            detailed, neff_b64, ntff_b64 = detailed_profile(batch, candidate, ms, warmup, iters, eps)
     except Exception as exc:  # noqa: BLE001 - every failure becomes a row
         hardware_output = capture_error(exc)
         summary = None
@@ -182,7 +183,49 @@ def benchmark_one(
         hardware_output=hardware_output,
         profiler_summary=summary,
         profile_detailed=detailed,
+        neff_b64=neff_b64,
+        ntff_b64=ntff_b64,
     )
+
+
+def detailed_profile(batch: DeviceBatch, candidate: Candidate, ms: list[float], warmup: int, iters: int, eps: float):
+    """The per-candidate detail a ``--detailed`` run keeps, and the two binary artefacts.
+
+    Upstream a detailed run stores the profiler's per-instruction JSON, the compiled binary
+    (``file.neff``) and the raw trace (``profile.ntff``) beside each candidate
+    (``autotune/src/autotune/runner/benchmark.py:81-84, 90-113, 141-143``).  These kernels need no
+    external profiler for the same questions: the library describes the launch (kernel variant,
+    grid, shared / tensor memory, waves of the persistent schedule, registers, the UMMA-issue-bound
+    cycles of the busiest CTA group) and the GEMM kernels report their own longest CTA lifetime in
+    SM cycles, so ``tensor_pipe_busy_estimate`` = bound / lifetime comes without ncu.  ``file.neff``
+    holds what identifies the executable -- the descriptor text and the raw ``b200_cfg`` -- and
+    ``profile.ntff`` the per-launch time series as little-endian float32.
+    Returns ``(profile.json dict, file.neff as base64, profile.ntff as base64)``.
+    """
+    import base64
+    import ctypes as C
+    import struct
+
+    from autotune import kernels, native
+
+    plan = native.describe_launch(batch.family, candidate.config, batch.M, batch.N, batch.K)
+    detail: dict[str, Any] = {"launches_ms": [float(x) for x in ms], "warmup": warmup, "iters": iters, "plan": plan}
+    if plan["kernel"].startswith("gemm_tcgen05_kernel"):
+        # one more launch that records its longest CTA lifetime (clock64 and globaltimer)
+        cfg = dict(candidate.config, _record_clocks=1)
+        batch.status.zero_()
+        kernels.time_kernel(batch.family, batch.a, batch.b, batch.out, cfg, gamma=batch.gamma, eps=eps,
+                            warmup=0, iters=1, status=batch.status)
+        st = batch.status.cpu().tolist()
+        batch.status.zero_()
+        if st[0] == 0 and st[6] > 0:
+            detail["cta_lifetime_sm_cycles"] = int(st[6])
+            detail["cta_lifetime_ns"] = int(st[7])
+            detail["tensor_pipe_busy_estimate"] = round(plan["umma_bound_sm_cycles"] / st[6], 4)
+    cfg_struct = native.Cfg.from_dict(candidate.config)
+    blob = b"B200CAND\x01" + bytes(C.string_at(C.byref(cfg_struct), C.sizeof(cfg_struct))) + candidate.to_source().encode()
+    series = struct.pack("<8sI", b"B200TIME", len(ms)) + struct.pack(f"<{len(ms)}f", *[float(x) for x in ms])
+    return detail, base64.b64encode(blob).decode(), base64.b64encode(series).decode()
 
 
 def _time_fp32(batch: DeviceBatch, warmup: int, iters: int) -> list[float]:

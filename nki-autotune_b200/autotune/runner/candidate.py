@@ -106,12 +106,18 @@ def enumerate_grid(
 def extended_grid(family: str, scalars: dict | None = None) -> list[Candidate]:
     """The 64-point grid followed by 24 large-tile points that use all 512 tensor-memory columns
     for one accumulator: 512x256 and 512x128 (CTA pair, two UMMAs along M), 256x512 (CTA pair, two
-    UMMAs along N) and 128x512 (single CTA), each with tile K in {64,128} and 2..4 stages."""
+    UMMAs along N) and 128x512 (single CTA), each with tile K in {64,128} and 2..4 stages; and by 6
+    points that vary the rasterisation swizzle (1, 4, 8) on the 512x256 and 256x512 tiles."""
     out = enumerate_grid(family, scalars=scalars)
     for (tm, tn, cm), tk, st in itertools.product(
             [(512, 256, 2), (512, 128, 2), (256, 512, 2), (128, 512, 1)], (64, 128), (2, 3, 4)):
         cfg = {"tile_m": tm, "tile_n": tn, "tile_k": tk, "stages": st, "cluster_m": cm, "cluster_n": 1,
                "swizzle": 0, "split_k": 0}
+        out.append(Candidate(family=family, config=cfg, scalars=dict(scalars or {})))
+    # the rasterisation group width as a dimension, on the two fastest tile shapes
+    for (tm, tn), sw in itertools.product([(512, 256), (256, 512)], (1, 4, 8)):
+        cfg = {"tile_m": tm, "tile_n": tn, "tile_k": 64, "stages": 4, "cluster_m": 2, "cluster_n": 1,
+               "swizzle": sw, "split_k": 0}
         out.append(Candidate(family=family, config=cfg, scalars=dict(scalars or {})))
     return out
 

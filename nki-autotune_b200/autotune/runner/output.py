@@ -187,8 +187,12 @@ def _write_per_kernel_profiles(cache_dir: str, results: list[ProfileResult]) -> 
                     fh.write(base64.b64decode(blob))
 
 
-def write_results_json(cache_dir: str, num_kernels: int, results: list[ProfileResult], wallclock_s: float) -> None:
-    """Write ``results.json`` and the per-candidate files (reference: output.py:218-271)."""
+def write_results_json(cache_dir: str, num_kernels: int, results: list[ProfileResult], wallclock_s: float,
+                       extra_metadata: dict | None = None) -> None:
+    """Write ``results.json`` and the per-candidate files (reference: output.py:218-271).
+
+    ``extra_metadata`` follows the two upstream metadata keys: what a reader needs to interpret the
+    numbers (GPU name, GPUs used, the peaks behind the MFU / MBU percentages, seed, tolerance)."""
     _write_per_kernel_profiles(cache_dir, results)
 
     rows = []
@@ -257,7 +261,7 @@ def write_results_json(cache_dir: str, num_kernels: int, results: list[ProfileRe
         "tmem_oom": counters["tmem_oom"],
     }
     doc = {
-        "metadata": {"num_kernels": num_kernels, "wallclock_s": wallclock_s},
+        "metadata": {"num_kernels": num_kernels, "wallclock_s": wallclock_s, **(extra_metadata or {})},
         "metrics": metrics,
         "kernels": index,
     }

@@ -815,6 +815,87 @@ extern "C" int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, l
   return rc;
 }
 
+// What a launch of this candidate at this shape looks like, as one JSON object: which kernel, grid,
+// cluster, threads, shared and tensor memory, tiles / CTA groups / waves of the persistent schedule,
+// the UMMA-issue-bound SM cycles of the busiest CTA group, and the compiled kernel's registers and
+// local memory.  No launch is made; without a usable device the device-derived fields are null.
+extern "C" int b200_describe_launch(const char* family, const b200_cfg* cfg_in, long M, long N, long K, char* out,
+                                    size_t out_bytes) {
+  if (!out || out_bytes == 0) return set_error(B200_ERR_BAD_ARG, "describe_launch: no output buffer");
+  Family fam = parse_family(family);
+  b200_cfg eff;
+  const b200_cfg* cfg = cfg_in;
+  if (fam == FAM_RMSNORM && M > SKINNY_ROWS && (!cfg || cfg->norm_mode != 1)) {
+    // what runs when scratch is supplied: the prologue variant of the plain GEMM
+    eff = cfg ? *cfg : default_cfg(FAM_LHST, M, N);
+    eff.norm_mode = 2;
+    cfg = &eff;
+  }
+  Plan plan;
+  memset(&plan, 0, sizeof(plan));
+  int rc = make_plan(fam, cfg, M, N, K, &plan);
+  if (rc) return rc;
+  DeviceInfo di;
+  const bool have_dev = device_info(&di) == B200_OK;
+  const long sms = have_dev ? di.sm_count : 148;
+  const void* kptr = nullptr;
+  const char* kname = "";
+  int threads = GEMM_THREADS;
+  if (plan.skinny) { kptr = reinterpret_cast<const void*>(rmsnorm_skinny_kernel); kname = "rmsnorm_skinny_kernel"; threads = SKINNY_THREADS; }
+  else if (fam == FAM_RMSNORM && !plan.prologue) { kptr = reinterpret_cast<const void*>(pick_rms_kernel(plan)); kname = "rmsnorm_tcgen05_kernel"; threads = RMS_THREADS; }
+  else { kptr = reinterpret_cast<const void*>(pick_gemm_kernel(plan)); kname = "gemm_tcgen05_kernel"; }
+  int regs = -1, local_bytes = -1;
+  if (have_dev) {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kptr) == cudaSuccess) { regs = fa.numRegs; local_bytes = static_cast<int>(fa.localSizeBytes); }
+    else (void)cudaGetLastError();
+  }
+  char regs_txt[32] = "null", local_txt[32] = "null";
+  if (regs >= 0) { snprintf(regs_txt, sizeof(regs_txt), "%d", regs); snprintf(local_txt, sizeof(local_txt), "%d", local_bytes); }
+  int n = 0;
+  if (plan.skinny) {
+    const long T = (N + SKINNY_TILE_N - 1) / SKINNY_TILE_N, nkb = (K + plan.tile_k - 1) / plan.tile_k;
+    long grid = sms > SKINNY_MAX_CTAS ? SKINNY_MAX_CTAS : sms;
+    if (T < grid && T * nkb < grid) grid = T * nkb;
+    n = snprintf(out, out_bytes,
+                 "{\"kernel\": \"%s\", \"grid\": %ld, \"cluster\": 1, \"threads\": %d, \"smem_bytes\": %ld, \"tmem_cols\": %d, "
+                 "\"stages\": %d, \"tile_k\": %d, \"tiles_256_columns\": %ld, \"k_blocks\": %ld, \"whole_tiles_per_cta\": %ld, "
+                 "\"shared_tiles\": %ld, \"sm_count\": %ld, \"sm_count_from_device\": %s, \"registers\": %s, \"local_bytes\": %s}",
+                 kname, grid, threads, plan.smem_bytes, plan.tmem_cols, plan.stages, plan.tile_k, T, nkb, T / grid, T % grid, sms,
+                 have_dev ? "true" : "false", regs_txt, local_txt);
+  } else {
+    const long m_tiles = (M + plan.tile_m - 1) / plan.tile_m, n_tiles = (N + plan.tile_n - 1) / plan.tile_n;
+    const long nkb = (K + plan.tile_k - 1) / plan.tile_k;
+    const long units = m_tiles * n_tiles * plan.split_k;
+    long groups = sms / plan.cluster;
+    const long per_group = plan.cta_group == 2 ? units : (units + plan.cluster - 1) / plan.cluster;
+    if (groups > per_group) groups = per_group;
+    if (cfg && cfg->reserved[3] > 0 && groups > cfg->reserved[3] / plan.cluster) groups = cfg->reserved[3] / plan.cluster;
+    if (groups < 1) groups = 1;
+    const long ctas = groups * plan.cluster;
+    const long streams = plan.cta_group == 2 ? groups : ctas;      // independent tile streams
+    const long rounds = (units + streams - 1) / streams;           // tiles the busiest stream works through
+    // one UMMA of 128 x tile_n x 16 per SM keeps the tensor pipe busy tile_n / 2 cycles (8192 dense
+    // bf16 FLOP per cycle and SM); a tile of one stream is m_sub of them per 16 k
+    const double umma_cycles = static_cast<double>(rounds) * (nkb / static_cast<double>(plan.split_k)) *
+                               (plan.tile_k / 16) * plan.m_sub * (plan.tile_n / 2.0);
+    n = snprintf(out, out_bytes,
+                 "{\"kernel\": \"%s<%d,%d,%s>\", \"grid\": %ld, \"cluster\": %d, \"threads\": %d, \"smem_bytes\": %ld, "
+                 "\"tmem_cols\": %d, \"acc_bufs\": %d, \"stages\": %d, \"tile\": [%d, %d, %d], \"group_m\": %d, \"split_k\": %d, "
+                 "\"tiles\": %ld, \"k_blocks\": %ld, \"cta_groups\": %ld, \"waves\": %.3f, \"tiles_of_busiest_group\": %ld, "
+                 "\"umma_bound_sm_cycles\": %.0f, \"x_ring\": {\"a_stages\": %d, \"a_slots\": %d, \"groups\": %d}, "
+                 "\"sm_count\": %ld, \"sm_count_from_device\": %s, \"registers\": %s, \"local_bytes\": %s}",
+                 kname, plan.cta_group, plan.m_sub,
+                 plan.prologue ? "norm" : (plan.a_kmajor ? "kmajor" : (fam == FAM_RMSNORM ? "inline" : "lhsT")), ctas, plan.cluster,
+                 threads, plan.smem_bytes, plan.tmem_cols, plan.acc_bufs, plan.stages, plan.tile_m, plan.tile_n, plan.tile_k,
+                 plan.group_m, plan.split_k, units, nkb, groups, static_cast<double>(units) / streams, rounds, umma_cycles,
+                 plan.a_stages, plan.a_slots, plan.groups, sms,
+                 have_dev ? "true" : "false", regs_txt, local_txt);
+  }
+  if (n < 0 || static_cast<size_t>(n) >= out_bytes) return set_error(B200_ERR_BAD_ARG, "describe_launch: buffer of %zu bytes is too small", out_bytes);
+  return B200_OK;
+}
+
 extern "C" int b200_default_cfg(const char* family, long M, long N, long K, b200_cfg* cfg) {
   (void)K;
   if (!cfg) return set_error(B200_ERR_BAD_ARG, "default_cfg: NULL pointer");

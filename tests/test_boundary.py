@@ -100,7 +100,8 @@ def test_candidate_round_trip_and_grid():
     grid = enumerate_grid("matmul_lhsT_rhs")
     assert len(grid) == 64 and len({tuple(sorted(g.config.items())) for g in grid}) == 64
     ext = extended_grid("matmul_lhsT_rhs")
-    assert len(ext) == 88 and ext[:64] == grid and len({tuple(sorted(g.config.items())) for g in ext}) == 88
+    assert len(ext) == 94 and ext[:64] == grid and len({tuple(sorted(g.config.items())) for g in ext}) == 94
+    assert sorted({g.config["swizzle"] for g in ext[88:]}) == [1, 4, 8]
     with pytest.raises(ValueError):
         parse_source("FAMILY = 'nope'\n")
     with pytest.raises(ValueError):
@@ -141,7 +142,28 @@ def test_cfg_check_budgets(native_lib):
     assert 0 < accepted < 64  # the grid holds both runnable and over-subscribed points
     big = [native.cfg_check("matmul_lhsT_rhs", c.config, 8192, 8192, 8192)[0] for c in extended_grid("matmul_lhsT_rhs")[64:]]
     assert native.OK in big and native.ERR_SMEM_OOM in big and set(big) <= {native.OK, native.ERR_SMEM_OOM}
-    print("accepted of the 64-point grid:", accepted, "of the 24 large-tile points:", big.count(native.OK))
+    print("accepted of the 64-point grid:", accepted, "of the 30 extra points:", big.count(native.OK))
+
+
+def test_describe_launch_reports_the_plan(native_lib):
+    """The launch description a detailed profile stores: schedule arithmetic checked by hand for
+    the headline shape (512 tiles over 74 CTA pairs = 6.92 waves, 7 tiles on the busiest pair,
+    7 x 128 k-blocks x 4 UMMA steps x 2 row blocks x 128 cycles)."""
+    from autotune import native
+
+    d = native.describe_launch("matmul_lhsT_rhs", dict(tile_m=512, tile_n=256, tile_k=64, stages=4, cluster_m=2), 8192, 8192, 8192)
+    assert d["kernel"] == "gemm_tcgen05_kernel<2,2,lhsT>" and d["cluster"] == 2 and d["tmem_cols"] == 512 and d["acc_bufs"] == 1
+    if not d["sm_count_from_device"]:
+        assert d["grid"] == 148 and d["cta_groups"] == 74 and d["tiles"] == 512 and d["tiles_of_busiest_group"] == 7
+        assert abs(d["waves"] - 512 / 74) < 1e-3 and d["umma_bound_sm_cycles"] == 7 * 128 * 4 * 2 * 128
+        assert d["registers"] is None
+    assert d["smem_bytes"] <= 232448
+    f = native.describe_launch("rmsnorm_matmul", None, 4096, 11008, 4096)
+    assert f["kernel"].endswith("norm>") and f["tiles"] == 8 * 43
+    sk = native.describe_launch("rmsnorm_matmul", None, 16, 28672, 8192)
+    assert sk["kernel"] == "rmsnorm_skinny_kernel" and sk["tiles_256_columns"] == 112
+    capped = native.describe_launch("matmul_lhsT_rhs", dict(tile_m=512, tile_n=256, tile_k=64, stages=4, cluster_m=2, _max_ctas=132), 8192, 8192, 8192)
+    assert capped["grid"] <= 132
 
 
 def test_split_k_validation_and_scratch(native_lib):

@@ -35,7 +35,17 @@ def test_profile_sweep_writes_reference_cache_layout(native_lib, tmp_path):
     assert (tmp_path / ok / f"{ok}.py").exists() and (tmp_path / ok / "log-neuron-cc.txt").exists()
     summary = json.loads((tmp_path / ok / "profile_summary.json").read_text())
     assert summary["max_abs_rel_err"] <= 1e-2 and summary["total_time"] > 0
-    assert (tmp_path / ok / "profile.json").exists()                     # detailed run
+    detail = json.loads((tmp_path / ok / "profile.json").read_text())    # detailed run: plan + kernel's own cycle count
+    assert detail["plan"]["kernel"].startswith("gemm_tcgen05_kernel") and detail["plan"]["registers"] > 0
+    assert detail["cta_lifetime_sm_cycles"] > 0 and 0 < detail["tensor_pipe_busy_estimate"] <= 1.0
+    assert len(detail["launches_ms"]) == 3
+    neff = (tmp_path / ok / "file.neff").read_bytes()                    # descriptor + raw b200_cfg
+    assert neff.startswith(b"B200CAND") and b"FAMILY = 'matmul_lhsT_rhs'" in neff
+    ntff = (tmp_path / ok / "profile.ntff").read_bytes()                 # per-launch time series
+    assert ntff.startswith(b"B200TIME") and len(ntff) == 12 + 4 * 3
+    meta = data["metadata"]
+    assert list(meta)[:2] == ["num_kernels", "wallclock_s"] and "B200" in meta["gpu_name"] and meta["seed"] == 1
+    assert meta["peaks"]["bf16_tflops"] > 0 and meta["tolerance"]["bf16_max_abs_rel_err"] == 1e-2 and meta["n_gpus"] >= 1
     text = str(out)
     assert "Succeeded:" in text and "failures:" in text
 
