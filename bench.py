@@ -231,8 +231,8 @@ def pick_config(kernels, a, b, out, status) -> tuple[dict, dict]:
 def autotune_sweep(ranks: "Ranks", torch, kernels, lhs_T_np, rhs_np, a, b, out) -> tuple[dict, dict]:
     """The autotune sweep at 8192^3 through the package's own ``profile()``: the 64-point grid plus
     the 24 large-tile points, candidates sharded over the ranks (candidate i of the accepted list
-    on rank i mod N, no collective), results gathered on the host, the five leaders timed again
-    on rank 0's GPU, back to back and interleaved.  Every rank passes the seeded inputs it already holds, so nothing is
+    on rank i mod N, no collective), results gathered on the host, the five leaders run again
+    on rank 0's GPU and the kernel's own cycle count picks among them.  Every rank passes the seeded inputs it already holds, so nothing is
     generated inside the sweep.  Returns (winning config for every rank, record for the JSON line)."""
     from autotune.runner.api import profile
     from autotune.runner.candidate import extended_grid, jobs_from_candidates, parse_source
@@ -267,20 +267,34 @@ def autotune_sweep(ranks: "Ranks", torch, kernels, lhs_T_np, rhs_np, a, b, out) 
             "per_rank": per_rank,
         }
         if flat:
-            # The leaders were timed on different GPUs (which differ by several percent under their
-            # power caps) and with a memset between launches.  The five fastest run again on this
-            # GPU the way the headline does -- launches back to back, no flush -- interleaved in one
-            # stream so that all five see the same clocks; that order decides.
+            # The leaders are within a percent or two of each other, they were timed on different GPUs
+            # (which differ by several percent under their power caps), and wall time on a GPU that
+            # has just run a sweep at its power cap depends on what ran before.  So the five fastest
+            # run again on this GPU and the kernel's own count decides: the longest CTA lifetime in
+            # SM cycles (clock64 inside the kernel), which does not move with the clock.  Their wall
+            # times (launches back to back, interleaved in one stream, so all five see the same
+            # clocks) are recorded beside it.
             leaders = [name for name, _, _ in flat[:5]]
             cfgs = {}
             for name in leaders:
                 c = parse_source(jobs[name].source).config
                 cfgs[name] = {k: int(v) for k, v in c.items() if k in ("tile_m", "tile_n", "tile_k", "stages", "cluster_m", "swizzle") and v}
             times = back_to_back(torch, [(lambda c: (lambda: kernels.matmul_lhsT_rhs(a, b, cfg=c, out=out)))(cfgs[n]) for n in leaders], rounds=20)
-            ranked = sorted(((n, statistics.median(t)) for n, t in zip(leaders, times)), key=lambda r: r[1])
-            record["leaders_retimed_back_to_back_on_rank0_ms"] = [[n, cfg_name(cfgs[n]), round(t, 4)] for n, t in ranked]
-            record["winner"] = ranked[0][0]
-            winner = cfgs[ranked[0][0]]
+            st = kernels.new_status()
+            cycles = {}
+            for n in leaders:
+                seen = []
+                for _ in range(7):
+                    st.zero_()
+                    kernels.matmul_lhsT_rhs(a, b, cfg=dict(cfgs[n], _record_clocks=1), out=out, status=st)
+                    seen.append(int(st.cpu()[6]))
+                cycles[n] = int(statistics.median(seen))
+            ranked = sorted(leaders, key=lambda n: cycles[n])
+            record["leaders_on_rank0"] = [
+                {"name": n, "config": cfg_name(cfgs[n]), "sm_cycles": cycles[n], "back_to_back_ms": round(statistics.median(t), 4)}
+                for n, t in sorted(zip(leaders, times), key=lambda nt: cycles[nt[0]])]
+            record["winner"] = ranked[0]
+            winner = cfgs[ranked[0]]
     winner = ranks.broadcast(winner)
     return winner, record
 
@@ -450,7 +464,7 @@ def run_ours(args) -> None:
             "workload": WORKLOAD,
             "per_gpu": "M=N=K=8192 (rows of a [8192*n_gpus]-row product, rhs replicated)",
             "kernel_config": cfg,
-            "chosen_by": "shortlist (--no-sweep)" if args.no_sweep else "autotune sweep (see sweep), five leaders re-timed back to back on rank 0",
+            "chosen_by": "shortlist (--no-sweep)" if args.no_sweep else "autotune sweep (see sweep); among its five leaders, the fewest SM cycles on rank 0",
             "l2": "inputs+output 384 MiB per launch exceed the 126 MB L2; no flush between steps",
             "cooldown_s_before_timed_region": args.cooldown,
             "peaks": peaks["source"],

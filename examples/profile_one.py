@@ -1,7 +1,8 @@
 """Profile ONE configuration of one kernel family, with the detailed artefacts.
 
-    python examples/profile_one.py --cache DIR [--family matmul_lhsT_rhs] [--size 8192]
+    python examples/profile_one.py --cache DIR [--family matmul_lhsT_rhs] [--size 8192 | --m M --k K --n N]
                                    [--tile-m 512 --tile-n 256 --tile-k 64 --stages 4 --cluster-m 2]
+                                   [--warmup 10 --iters 50]
 
 Counterpart of ``examples/profile_hand_90mfu.py:35-45`` upstream (one hand-tuned kernel through
 ``profile(..., collect_detailed_profile=True)``).  The cache directory then holds, beside the
@@ -30,6 +31,12 @@ def main() -> None:
     ap.add_argument("--cache", required=True)
     ap.add_argument("--family", default="matmul_lhsT_rhs", choices=("matmul_lhsT_rhs", "matmul_lhs_rhs", "rmsnorm_matmul"))
     ap.add_argument("--size", type=int, default=8192, help="K = M = N (rmsnorm_matmul: x[size, size] . w[size, size])")
+    ap.add_argument("--m", type=int, default=0, help="rows of the result (overrides --size)")
+    ap.add_argument("--k", type=int, default=0, help="contraction length (overrides --size)")
+    ap.add_argument("--n", type=int, default=0, help="columns of the result (overrides --size)")
+    ap.add_argument("--eps", type=float, default=1e-6)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--tile-m", type=int, default=512)
     ap.add_argument("--tile-n", type=int, default=256)
     ap.add_argument("--tile-k", type=int, default=64)
@@ -38,22 +45,23 @@ def main() -> None:
     ap.add_argument("--norm-mode", type=int, default=0)
     args = ap.parse_args()
 
-    n = args.size
-    d = {"kind": "normal", "scale": n ** -0.5}
+    m, k, n = args.m or args.size, args.k or args.size, args.n or args.size
+    d = {"kind": "normal", "scale": k ** -0.5}
     if args.family == "matmul_lhsT_rhs":
-        specs, scalars = {"lhs_T": ((n, n), "bfloat16", d), "rhs": ((n, n), "bfloat16", d)}, {}
+        specs, scalars = {"lhs_T": ((k, m), "bfloat16", d), "rhs": ((k, n), "bfloat16", d)}, {}
     elif args.family == "matmul_lhs_rhs":
-        specs, scalars = {"lhs": ((n, n), "bfloat16", d), "rhs": ((n, n), "bfloat16", d)}, {}
+        specs, scalars = {"lhs": ((m, k), "bfloat16", d), "rhs": ((k, n), "bfloat16", d)}, {}
     else:
-        specs = {"x": ((n, n), "bfloat16"), "gamma": ((n,), "bfloat16", {"kind": "uniform", "low": 0.5, "high": 1.5}),
-                 "weight": ((n, n), "bfloat16", d)}
-        scalars = {"eps": 1e-6}
+        specs = {"x": ((m, k), "bfloat16"), "gamma": ((k,), "bfloat16", {"kind": "uniform", "low": 0.5, "high": 1.5}),
+                 "weight": ((k, n), "bfloat16", d)}
+        scalars = {"eps": args.eps}
     cfg = dict(tile_m=args.tile_m, tile_n=args.tile_n, tile_k=args.tile_k, stages=args.stages, cluster_m=args.cluster_m,
                norm_mode=args.norm_mode)
     cache_dir = os.path.join(args.cache, "profile_one")
     shutil.rmtree(cache_dir, ignore_errors=True)
-    jobs = jobs_from_candidates([Candidate(args.family, cfg, scalars)], (n, n), specs)
-    out = profile(jobs, cache_dir=cache_dir, seed=1, neuron_platform_target="b200", collect_detailed_profile=True, n_gpus=1)
+    jobs = jobs_from_candidates([Candidate(args.family, cfg, scalars)], (m, n), specs)
+    out = profile(jobs, cache_dir=cache_dir, seed=1, neuron_platform_target="b200", collect_detailed_profile=True, n_gpus=1,
+                  warmup=args.warmup, iters=args.iters)
     print(out)
     stem = next(iter(jobs))[:-3]
     detail = Path(cache_dir) / stem / "profile.json"

@@ -35,12 +35,18 @@ def test_noalloc_entry_matches_workspace_entry_twice_in_a_row(native_lib):
         ref = kernels.rmsnorm_matmul(x, g, w, eps=1e-5)                      # existing entry point, caller workspace
         out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
         status = kernels.new_status()
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        # free device memory as the driver sees it: an allocation made inside the library (which
+        # torch's own counters cannot see) would show up here.  The first call may still load the
+        # kernel's module lazily, so the comparison is made on the second, warm call.
+        free_before, _ = torch.cuda.mem_get_info()
         rc = lib.b200_rmsnorm_matmul_noalloc(x.data_ptr(), g.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
                                              C.c_float(1e-5), None, status.data_ptr(), stream)
         assert rc == native.OK, native.last_error()
-        assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        if call == 1:
+            assert free_after >= free_before, f"the call took {free_before - free_after} bytes of device memory"
         kernels.raise_on_status(status)
         a = kernels.to_host(out).astype(np.float32)
         r = kernels.to_host(ref).astype(np.float32)
