@@ -620,6 +620,10 @@ static int prepare(const LaunchArgs& la, const b200_cfg* cfg, int* dev_status, P
   gp.kb_per_part = plan.split_k > 1 ? plan.kb_per_part : gp.num_k_blocks;
   gp.part_rows = static_cast<int>((la.M + plan.tile_m - 1) / plan.tile_m * plan.tile_m);
   gp.acc_bufs = plan.acc_bufs;
+  // a single-buffered accumulator of exactly two UMMA blocks is handed over in halves (not with
+  // split-K, whose epilogue stores the whole fp32 tile)
+  gp.acc_halves = (plan.acc_bufs == 1 && plan.split_k <= 1 &&
+                   ((plan.m_sub == 2 && plan.tile_n <= 256) || (plan.m_sub == 1 && plan.tile_n == 512))) ? 1 : 0;
   gp.tmem_cols = plan.tmem_cols;
   gp.ld_out = la.ld_out;
   gp.out = static_cast<__nv_bfloat16*>(la.out);

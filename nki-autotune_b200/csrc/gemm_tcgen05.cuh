@@ -67,6 +67,8 @@ struct GemmParams {
   int num_k_blocks;
   int group_m;       // rasterisation group width (tiles along M)
   int acc_bufs;      // accumulator buffers in tensor memory: 1 or 2
+  int acc_halves;    // 1: a single-buffered accumulator of two UMMA blocks (two row blocks, or two 256-column
+                     // blocks) is handed over in halves, each with its own full / empty barrier (see the issuer)
   int tmem_cols;     // allocation size (power of two >= 32)
   long long ld_out;  // elements
   __nv_bfloat16* out;
@@ -369,6 +371,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
         const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc_sub;  // first UMMA's share; next at + umma_n
+        // the loads of one stage
+        auto arm_stage = [&](uint32_t s) {
+          const uint32_t full_local = smem_u32(&ctrl->full[s]);
+          if constexpr (PAIR) {
+            if (cta_rank == 0) mbar_arrive_expect_tx_elect(full_local, 2u * (a_bytes + b_bytes));
+          } else {
+            mbar_arrive_expect_tx_elect(full_local, a_bytes + b_bytes);
+          }
+        };
+        auto load_a = [&](uint32_t s, int kb) {
+          const uint32_t a_s = a_base + s * a_bytes;
+          const int k0 = kb * tile_k;
+          const uint32_t full_local = smem_u32(&ctrl->full[s]);
+          if constexpr (PAIR) {
+            const uint32_t full_leader = map_to_cta(full_local, 0);
+            if constexpr (A_KMAJOR) {
+              for (int c = 0; c < tile_k / 64; ++c)
+                tma_load_2d_pair_elect(a_s + c * MC * 128, &tm_a, full_leader, k0 + 64 * c, m_base);
+            } else {
+              for (int c = 0; c < MC / 64; ++c)
+                tma_load_2d_pair_elect(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
+            }
+          } else {
+            if constexpr (A_KMAJOR) {
+              for (int c = 0; c < tile_k / 64; ++c)
+                tma_load_2d_elect(a_s + c * MC * 128, &tm_a, full_local, k0 + 64 * c, m_base);
+            } else {
+              for (int c = 0; c < MC / 64; ++c)
+                tma_load_2d_elect(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
+            }
+          }
+        };
+        auto load_b = [&](uint32_t s, int kb) {
+          const uint32_t b_s = b_base + s * b_bytes;
+          const int k0 = kb * tile_k;
+          const uint32_t full_local = smem_u32(&ctrl->full[s]);
+          // B chunks of 64 columns; after this CTA's share of one UMMA the column jumps to the next UMMA
+          if constexpr (PAIR) {
+            const uint32_t full_leader = map_to_cta(full_local, 0);
+            for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
+              tma_load_2d_pair_elect(b_s + c * tile_k * 128, &tm_b, full_leader, col, k0);
+              col += 64;
+              if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
+            }
+          } else {
+            for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
+              tma_load_2d_elect(b_s + c * tile_k * 128, &tm_b, full_local, col, k0);
+              col += 64;
+              if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
+            }
+          }
+        };
         if constexpr (NORM) {
           if (p.xg != nullptr) {  // A = xg: this CTA's rows of the tile must have been written
             for (int blk = m_base / NORM_BLOCK; blk * NORM_BLOCK < min(m_base + MC, p.M) && ok; ++blk)
@@ -388,47 +442,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           ok = bounded_wait<false>(wctx, smem_u32(&ctrl->empty[s]), ph ^ 1u, 100 + s, tile, kb);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          const uint32_t a_s = a_base + s * a_bytes;
-          const uint32_t b_s = b_base + s * b_bytes;
-          const int k0 = kb * tile_k;
-          const uint32_t full_local = smem_u32(&ctrl->full[s]);
 #ifdef B200_MEASURE_HOOKS
           if (p.debug_mode == DEBUG_NO_RELOAD && it >= static_cast<uint32_t>(stages)) {
             // operands stay as first loaded, only the barrier protocol runs
-            if (!PAIR || cta_rank == 0) mbar_arrive_elect(full_local);
-          } else
-#endif
-          if constexpr (PAIR) {
-            const uint32_t full_leader = map_to_cta(full_local, 0);
-            if (cta_rank == 0) mbar_arrive_expect_tx_elect(full_local, 2u * (a_bytes + b_bytes));
-            if constexpr (A_KMAJOR) {
-              for (int c = 0; c < tile_k / 64; ++c)
-                tma_load_2d_pair_elect(a_s + c * MC * 128, &tm_a, full_leader, k0 + 64 * c, m_base);
-            } else {
-              for (int c = 0; c < MC / 64; ++c)
-                tma_load_2d_pair_elect(a_s + c * tile_k * 128, &tm_a, full_leader, m_base + 64 * c, k0);
-            }
-            // B chunks of 64 columns; after this CTA's share of one UMMA the column jumps to the next UMMA
-            for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
-              tma_load_2d_pair_elect(b_s + c * tile_k * 128, &tm_b, full_leader, col, k0);
-              col += 64;
-              if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
-            }
-          } else {
-            mbar_arrive_expect_tx_elect(full_local, a_bytes + b_bytes);
-            if constexpr (A_KMAJOR) {
-              for (int c = 0; c < tile_k / 64; ++c)
-                tma_load_2d_elect(a_s + c * MC * 128, &tm_a, full_local, k0 + 64 * c, m_base);
-            } else {
-              for (int c = 0; c < MC / 64; ++c)
-                tma_load_2d_elect(a_s + c * tile_k * 128, &tm_a, full_local, m_base + 64 * c, k0);
-            }
-            for (int c = 0, col = n_base, in_sub = 0; c < b_chunks; ++c) {
-              tma_load_2d_elect(b_s + c * tile_k * 128, &tm_b, full_local, col, k0);
-              col += 64;
-              if (++in_sub == sub_chunks) { in_sub = 0; col += sub_jump; }
-            }
+            if (!PAIR || cta_rank == 0) mbar_arrive_elect(smem_u32(&ctrl->full[s]));
+            continue;
           }
+#endif
+          arm_stage(s);
+          load_a(s, kb);
+          load_b(s, kb);
         }
       }
       // tail: every stage released, so no UMMA-completion arrival is still on its way to
@@ -456,12 +479,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       const uint32_t nsub_step = (static_cast<uint32_t>(nc_sub / 64) * mn_lbo) >> 4;  // next UMMA's B chunks
       const int nk16 = tile_k / 16;
 #ifdef B200_MEASURE_HOOKS
-      const bool issue = p.debug_mode != DEBUG_NO_MMA;
+      const bool issue_enabled = p.debug_mode != DEBUG_NO_MMA;
 #else
-      constexpr bool issue = true;
+      constexpr bool issue_enabled = true;
 #endif
       Ring ring, acc;
       bool ok = true;
+      // A single-buffered accumulator made of two UMMA blocks (512x256: two row blocks; 256x512: two
+      // 256-column blocks) is handed over in halves: the tile's last k-block issues all of half 0's
+      // UMMAs first and commits half 0, so the epilogue drains half 0 while half 1's UMMAs still run;
+      // the next tile's first k-block issues half 0 as soon as half 0 is drained and half 1 after
+      // that.  Barriers acc_full[h] / acc_empty[h] then stand for half h (with one buffer, index 1 is
+      // free for that), and both flip once per tile.
+      const bool halves = p.acc_halves != 0;
+      const auto commit_to = [&](uint64_t* bar) {
+        if constexpr (PAIR) umma_commit_pair_elect(smem_u32(bar), 3);
+        else umma_commit_1cta_elect(smem_u32(bar));
+      };
       for (int unit = first_tile; unit < total_tiles && ok; unit += tile_stride, acc.advance(acc_bufs)) {
         const int tile = unit / split_k, part = unit - tile * split_k;
         const int kb0 = part * p.kb_per_part, kb1 = min(kb0 + p.kb_per_part, num_k_blocks);
@@ -487,37 +521,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (lane == 0 && unit == first_tile + 3 * tile_stride && kb == kb0) g_gemm_trace[blockIdx.x * 16 + 9] = clock64();
 #endif
           tc_fence_after();
-          uint64_t adesc = a_desc0 + s * a_step;
-          uint64_t bdesc = b_desc0 + s * b_step;
-          // one k-block of UMMAs; NS (instructions side by side along N) is a compile-time constant so
-          // that the common NS = 1 loop unrolls into a straight run of instructions
-          auto issue_k_block = [&](auto ns_const) {
+          const uint64_t adesc0 = a_desc0 + s * a_step;
+          const uint64_t bdesc0 = b_desc0 + s * b_step;
+          // One k-block of UMMAs.  NS (instructions side by side along N) is a compile-time constant so
+          // that the common NS = 1 loop unrolls into a straight run of instructions; HALF = -1 issues
+          // every block of the tile (16 k at a time), HALF = 0 / 1 only that half of the accumulator.
+          auto issue_k_block = [&](auto ns_const, auto half_const) {
             constexpr int NS = decltype(ns_const)::value;
+            constexpr int HALF = decltype(half_const)::value;
+            uint64_t adesc = adesc0, bdesc = bdesc0;
 #pragma unroll 4
             for (int k16 = 0; k16 < nk16; ++k16, adesc += 128, bdesc += 128) {
 #pragma unroll
               for (int mi = 0; mi < M_SUB; ++mi) {
+                if (HALF >= 0 && M_SUB == 2 && mi != HALF) continue;
                 uint64_t ad = adesc + mi * sub_step;
                 if constexpr (A_KMAJOR)  // K-major x tile: 64-wide k chunks of MC rows x 128 B, 32 B per 16 k
                   ad = make_smem_desc_sw128(a_base + s * a_bytes + (k16 >> 2) * (MC * 128) + mi * (128 * 128) +
                                                 (k16 & 3) * 32, 16, 1024);
 #pragma unroll
-                for (int ns = 0; ns < NS; ++ns)
+                for (int ns = 0; ns < NS; ++ns) {
+                  if (HALF >= 0 && M_SUB == 1 && ns != HALF) continue;
                   umma_bf16_elect<CTA_GROUP>(d_tmem + static_cast<uint32_t>(mi * tile_n + ns * umma_n), ad,
                                        bdesc + ns * nsub_step, idesc, ((kb - kb0) | k16) != 0 ? 1u : 0u);
+                }
               }
             }
           };
-          if (issue) {
-            if (n_sub == 1) issue_k_block(std::integral_constant<int, 1>{});
-            else issue_k_block(std::integral_constant<int, 2>{});
+          auto issue = [&](auto half_const) {
+            if (!issue_enabled) return;
+            if (n_sub == 1) issue_k_block(std::integral_constant<int, 1>{}, half_const);
+            else issue_k_block(std::integral_constant<int, 2>{}, half_const);
+          };
+          if (halves && (kb == kb0 || kb == kb1 - 1)) {
+            // first and / or last k-block of the tile: half by half
+            if (kb == kb0) {  // (half 0 was waited for above)
+              issue(std::integral_constant<int, 0>{});
+              if (kb == kb1 - 1) commit_to(&ctrl->acc_full[0]);
+              ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_empty[1]), acc.ph ^ 1u, 201, tile, -1);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              tc_fence_after();
+              issue(std::integral_constant<int, 1>{});
+            } else {
+              issue(std::integral_constant<int, 0>{});
+              commit_to(&ctrl->acc_full[0]);
+              issue(std::integral_constant<int, 1>{});
+            }
+          } else {
+            issue(std::integral_constant<int, -1>{});
           }
-          if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->empty[s]), 3);
-          else umma_commit_1cta_elect(smem_u32(&ctrl->empty[s]));
+          commit_to(&ctrl->empty[s]);
         }
         if (!ok) break;
-        if constexpr (PAIR) umma_commit_pair_elect(smem_u32(&ctrl->acc_full[b]), 3);
-        else umma_commit_1cta_elect(smem_u32(&ctrl->acc_full[b]));
+        commit_to(&ctrl->acc_full[halves ? 1 : b]);
 #ifdef B200_MEASURE_HOOKS
         if (lane == 0 && unit == first_tile + 2 * tile_stride) g_gemm_trace[blockIdx.x * 16 + 1] = clock64();
         if constexpr (NORM) {
@@ -573,6 +630,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
           row_scale[mi] = row < p.M ? __ldcg(p.rinv + row) : 0.0f;
         }
       }
+      const bool halves = p.acc_halves != 0;  // then b == 0 and acc_full[h] / acc_empty[h] stand for half h
       ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_full[b]), aph, 500 + b, tile, -1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -585,7 +643,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
 #endif
       tc_fence_after();
-      auto release_accumulator = [&]() {
+      auto release_accumulator = [&](int which) {
         // every tensor-memory load of this warp has completed (tcgen05.wait::ld): the issuer may
         // overwrite the accumulator.  No data in memory is handed over with this arrival, so the
         // remote form needs no release fence (which costs about 2000 cycles here).
@@ -595,8 +653,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (tr) g_gemm_trace[tr0 + 1] = clock64();
 #endif
         if (lane == 0) {
-          if constexpr (PAIR) mbar_arrive_cluster_relaxed(acc_empty_leader + b * 8);
-          else mbar_arrive(acc_empty_leader + b * 8);
+          if constexpr (PAIR) mbar_arrive_cluster_relaxed(acc_empty_leader + which * 8);
+          else mbar_arrive(acc_empty_leader + which * 8);
         }
 #ifdef B200_MEASURE_HOOKS
         if (tr) g_gemm_trace[tr0 + 2] = clock64();
@@ -639,7 +697,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             }
           }
         }
-        release_accumulator();
+        release_accumulator(b);
       } else {
         // Phase 1: all of this warp's chunks (at most four: two per 128-row block, or four of a
         // 512-column tile) go from tensor memory to registers as packed bf16, 64 accumulator
@@ -657,6 +715,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
           for (int ci = 0; ci < PER_MI; ++ci) {
             const int c = eg + ci * (EPI_WARPS / 4);
+            // accumulator handed over in halves: slots 0, 1 are half 0 (row block 0, or columns 0..255
+            // of a 512-column tile), slots 2, 3 half 1.  Before the first chunk of half 1: half 0 goes
+            // back to the issuer, and half 1 has to be complete.
+            if (mi * PER_MI + ci == SLOTS / 2 && halves) {
+              release_accumulator(0);
+              ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_full[1]), aph, 501, tile, -1);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              tc_fence_after();
+            }
             if (c < tile_n / 64) {
               const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                      static_cast<uint32_t>(b * acc_cols + mi * tile_n + c * 64);
@@ -672,8 +740,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
               }
             }
           }
+          if (!ok) break;
         }
-        release_accumulator();
+        if (!ok) break;
+        release_accumulator(halves ? 1 : b);
 #pragma unroll
         for (int mi = 0; mi < M_SUB; ++mi) {
           const int row0 = m_base + mi * 128 + q * 32;  // first of this warp's 32 rows
