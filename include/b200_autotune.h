@@ -67,7 +67,9 @@ typedef struct b200_cfg {
                      [2] 1 = GEMM kernel stores its longest CTA lifetime in dev_status[6] (SM cycles)
                      and [7] (nanoseconds); [3] > 0 = cap on the GEMM kernels' grid in CTAs (the
                      persistent schedule deals the tiles to fewer CTAs), for callers that run
-                     another kernel, e.g. a collective, beside it                              */
+                     another kernel, e.g. a collective, beside it; [4] 1 = the M <= 16 fused
+                     kernel is launched without the programmatic-dependent-launch attribute
+                     (see b200_rmsnorm_matmul)                                                  */
 } b200_cfg;
 
 /* Number of ints in a dev_status block (device memory, caller-owned, zeroed by caller).
@@ -145,7 +147,12 @@ int b200_matmul_lhsT_rhs_f32(const void* lhsT, const void* rhs, void* out,
  * cfg apply) and needs b200_workspace_bytes of zero-filled scratch (partial tiles of the
  * 256-column tiles that are shared between CTAs, and their counters); M > 16 see b200_cfg.norm_mode.
  * Replaces rmsnorm_matmul_online, kernel_library/rmsnorm_matmul/kernel_hand_online.py:198-353
- * (gamma is an extension; gamma == NULL reproduces that kernel's maths). */
+ * (gamma is an extension; gamma == NULL reproduces that kernel's maths).
+ * The M <= 16 kernel is a programmatic dependent launch: it may begin, and stream w, while the
+ * kernel launched before it on the same stream is still finishing; it waits for that kernel before it
+ * reads x or gamma, touches the workspace or writes out.  So w must not be written by the kernel
+ * launched immediately before this call on `stream` (weights are static in the decode loops this
+ * kernel is for); if it is, set b200_cfg.reserved[4] = 1 and the launch is an ordinary one. */
 int b200_rmsnorm_matmul(const void* x, const void* gamma, const void* w, void* out,
                         long M, long N, long K, float eps,
                         const b200_cfg* cfg, void* workspace, size_t workspace_bytes,

@@ -41,6 +41,7 @@ class Cfg(C.Structure):
         cfg.reserved[1] = int(d.get("_wait_limit_us", 0))
         cfg.reserved[2] = int(d.get("_record_clocks", 0))
         cfg.reserved[3] = int(d.get("_max_ctas", 0))
+        cfg.reserved[4] = int(d.get("_serial_launch", 0))
         return cfg
 
 

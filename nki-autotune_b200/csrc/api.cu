@@ -452,6 +452,7 @@ struct Prepared {
   SkinnyParams sp;
   bool fused;
   bool skinny;
+  bool skinny_serial;        // skinny kernel launched without the programmatic-dependent-launch attribute
   Plan plan;
   dim3 grid, block;
   size_t smem;
@@ -517,6 +518,7 @@ static int prepare_skinny(const LaunchArgs& la, const b200_cfg* cfg, const Plan&
   if (cfg && cfg->reserved[1] > 0) limit_us = cfg->reserved[1];
   sp.timeout_cycles = limit_us * (di.clock_khz > 0 ? di.clock_khz / 1000 : 1900);
   pr->skinny = true;
+  pr->skinny_serial = cfg != nullptr && cfg->reserved[4] != 0;
   pr->fused = false;
   pr->plan = plan;
   pr->smem = static_cast<size_t>(plan.smem_bytes);
@@ -776,8 +778,17 @@ static int launch(const Prepared& pr, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
-  if (pr.skinny)
+  if (pr.skinny) {
+    // programmatic dependent launch (see rmsnorm_skinny.cuh): the kernel waits by itself for the
+    // kernel before it wherever it depends on it, and streams its weights meanwhile
+    cudaLaunchAttribute sk_attr[2];
+    sk_attr[0] = attr[0];
+    sk_attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    sk_attr[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = sk_attr;
+    lc.numAttrs = pr.skinny_serial ? 1 : 2;
     return check_cuda(cudaLaunchKernelEx(&lc, rmsnorm_skinny_kernel, pr.tm_b, pr.sp), "skinny RMSNorm GEMM launch");
+  }
   if (pr.fused)
     return check_cuda(cudaLaunchKernelEx(&lc, pr.rms_fn, pr.tm_a, pr.tm_b, pr.rp), "fused RMSNorm GEMM launch");
   int rc = check_cuda(cudaLaunchKernelEx(&lc, pr.fn, pr.tm_a, pr.tm_b, pr.tm_out, pr.gp), "tcgen05 GEMM launch");

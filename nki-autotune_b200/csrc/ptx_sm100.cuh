@@ -35,6 +35,18 @@ __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while the kernel before it in the stream is still running, once every CTA of
+// that kernel has called grid_launch_dependents() (or exited); it must call grid_dependency_wait()
+// before it touches anything that kernel may have written.  Without the attribute, or after a kernel
+// that never signals, both are no-ops in effect.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

@@ -26,6 +26,12 @@
 //     rinv[m] for itself from x (L2).
 //   * the TMA producer warp initialises the barriers itself and starts loading at once; the
 //     other warps join through a named barrier after the tensor-memory allocation.
+//   * launched as a programmatic dependent launch: the weights are not produced by the kernel
+//     before this one in the stream, so the producer streams them without waiting for it, while
+//     every warp that reads x or gamma, touches the scratch or writes out first waits for that
+//     kernel to complete.  In a chain of these launches (a decode loop) a CTA's SM is taken by the
+//     next launch as soon as the CTA exits, and the next launch's first weight tiles are already
+//     in shared memory when the previous launch ends.
 //
 // Same maths as kernel_library/rmsnorm_matmul/kernel_hand_online.py:5-17 (plus gamma); the
 // per-row factor is applied after the K sum.  All waits are bounded (see gemm_tcgen05.cuh).
@@ -215,6 +221,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
   // The producer warp initialises the barriers and goes straight to its loads (it needs nothing
   // else); the other nine warps wait for that and for the tensor-memory allocation at a named
   // barrier the producer only arrives at.
+  grid_launch_dependents();  // the launch after this one may take SMs as this one's CTAs leave them
   if (warp == 0) {
     if (lane == 0) {
       ctrl->abort_flag = 0;
@@ -343,6 +350,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
     const uint32_t tmem_base = ctrl->tmem_base;
     const int q = warp & 3;          // tensor-memory lane quadrant
     const int et = (warp - 2) * 32 + lane;  // 0..127
+    grid_dependency_wait();  // x, the scratch and out may belong to the kernel before this one
     // rinv[m] for every row, from x itself: 8 threads per row, 16-byte loads, shuffle reduction
     {
       const int row = et >> 3, part = et & 7;
@@ -556,6 +564,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       }
     };
     uint4 cur_x[2], cur_g[2], nxt_x[2], nxt_g[2];
+    grid_dependency_wait();  // x and gamma may be produced by the kernel before this one
     SkinnyWork work(p);
     int kb_next = 0;
     bool have = work.next_unit(kb_next);

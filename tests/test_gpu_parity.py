@@ -310,6 +310,28 @@ def test_rmsnorm_skinny_work_splits(K, m, k, n):
         assert O.max_abs_rel_err(got, expect) <= TOL_BF16
 
 
+def test_rmsnorm_skinny_chain_of_dependent_launches(K):
+    """The weight-streaming kernel is a programmatic dependent launch: in a chain it starts (and
+    streams its weights) while its predecessor finishes, and waits for it before touching x, the
+    scratch or out.  A chain whose launches alternate between two activations and three weight
+    copies, every launch on the scratch its predecessor just used, must give each launch's own
+    result; so must the same chain launched the ordinary way."""
+    import torch
+
+    m, k, n = 16, 1024, 9472
+    t = O.generate_inputs(24, [("x", (m, k), None), ("gamma", (k,), U), ("weight", (k, n), N_(k))], bf16=True)
+    xs = [K.to_device(t["x"].astype(BF)), K.to_device((t["x"] * 0.5).astype(BF))]
+    g = K.to_device(t["gamma"].astype(BF))
+    ws = [K.to_device(t["weight"].astype(BF)) for _ in range(3)]
+    expect = [O.rmsnorm_matmul(t["x"] * s, t["gamma"], t["weight"], 1e-5) for s in (1.0, 0.5)]
+    torch.cuda.synchronize()
+    for c in (None, dict(tile_m=16, tile_n=256, tile_k=128, stages=3, _serial_launch=1)):
+        outs = [K.rmsnorm_matmul(xs[i % 2], g, ws[i % 3], eps=1e-5, cfg=c) for i in range(12)]
+        torch.cuda.synchronize()
+        for i, o in enumerate(outs):
+            assert O.max_abs_rel_err(K.to_host(o).astype(np.float32), expect[i % 2]) <= TOL_BF16, (c, i)
+
+
 def test_rmsnorm_skinny_counters_are_left_zero_and_slots_need_no_clearing(K):
     """The scratch starts with one counter per 256-column tile (zero between launches); the
     partial-tile slots behind them are written before they are read, so stale contents are harmless."""
