@@ -289,3 +289,29 @@ def test_generate_tensors_follows_reference_recipe():
     assert np.array_equal(got["lhs_T"], rng.standard_normal((8, 4)).astype(np.float32))
     assert np.array_equal(got["rhs"], rng.standard_normal((8, 6)).astype(resolve_dtype("bfloat16")))
     assert np.array_equal(got["g"], rng.uniform(0.5, 1.5, (6,)).astype(np.float32))
+
+
+def test_host_pipeline_has_no_cpu_path_and_numa_lookup_is_harmless():
+    """Without a GPU the host-buffer pipeline refuses to exist (there is no CPU fallback), and the
+    NUMA helpers answer "unknown" instead of raising."""
+    import torch
+
+    from autotune import pipeline
+    from autotune.native import NativeError
+
+    if not torch.cuda.is_available():
+        with pytest.raises(NativeError, match="no CPU path"):
+            pipeline.HostPipeline(64, 64, 64)
+        assert pipeline.bind_to_gpu_numa_node(0) == {"numa_node": None, "bound": False}
+
+
+def test_cyclic_rows_cover_c_once():
+    from autotune.sharded import cyclic_rows
+
+    for M, world, chunks in [(131072, 8, 8), (4096, 2, 4), (192, 3, 1)]:
+        pieces = sorted(p for r in range(world) for p in cyclic_rows(M, r, world, chunks))
+        assert pieces[0][0] == 0 and pieces[-1][1] == M
+        assert all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+        assert len({b - a for a, b in pieces}) == 1 and (pieces[0][1] - pieces[0][0]) % 8 == 0
+    with pytest.raises(ValueError):
+        cyclic_rows(1000, 0, 3, 2)
