@@ -93,6 +93,19 @@ int b200_device_count(int* count);
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
                    long* smem_bytes, int* tmem_cols);
 
+/* The checked build (libb200_autotune_checked.so, compiled with -DB200_CHECKED_BUILD; the same
+ * entry points, for debugging, several times slower): every shared-memory, tensor-memory and
+ * barrier address, every TMA coordinate and the kernels' global and schedule indices are
+ * validated on the device before use.  A failed check records its code, source line, value and
+ * limit and the access is skipped -- nothing traps, nothing out of range is touched; a skipped
+ * load leaves its consumer to the bounded wait (B200_ERR_DEVICE_WAIT).  This call synchronises
+ * the device and returns out4 = {failed checks, first failure's code << 32 | line, its value, its
+ * limit}; flags: 1 = clear the record afterwards, 2 = first run a self-test that passes
+ * out-of-range arguments to the checks (all refused: 96 failures).  In the normal library it
+ * returns B200_ERR_UNSUPPORTED and zeros.  Stands where the reference leans on its simulator's
+ * loud legality errors (nkigym/src/nkigym/ops/base.py:191-215). */
+int b200_checked_build_report(long long* out4, int flags);
+
 /* Describes, without launching anything, what a launch of this candidate at this shape is: one
  * JSON object in out[out_bytes] (NUL-terminated) with the kernel variant, grid, cluster, threads,
  * shared-memory bytes, tensor-memory columns, tiles / CTA groups / waves of the persistent schedule,

@@ -86,6 +86,7 @@ SIGNATURES = {
         [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long, C.POINTER(C.c_long), C.POINTER(C.c_int)],
     ),
     "b200_describe_launch": (C.c_int, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long, C.c_char_p, C.c_size_t]),
+    "b200_checked_build_report": (C.c_int, [C.POINTER(C.c_longlong), C.c_int]),
     "b200_default_cfg": (C.c_int, [C.c_char_p, C.c_long, C.c_long, C.c_long, C.POINTER(Cfg)]),
     "b200_workspace_bytes": (C.c_size_t, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long]),
     "b200_matmul_lhsT_rhs": (
@@ -181,6 +182,24 @@ def describe_launch(family: str, cfg: dict | None, M: int, N: int, K: int) -> di
     c = Cfg.from_dict(cfg)
     check(load().b200_describe_launch(family.encode(), C.byref(c) if c is not None else None, M, N, K, buf, len(buf)))
     return json.loads(buf.value.decode())
+
+
+CHECK_CODES = {1: "shared-memory range", 2: "barrier address", 3: "TMA load", 4: "TMA store", 5: "tensor-memory address",
+               6: "global index", 7: "schedule index"}
+
+
+def checked_build_report(clear: bool = True, selftest: bool = False) -> dict | None:
+    """The device-side check record of the checked build (``libb200_autotune_checked.so``, selected
+    with ``B200_AUTOTUNE_LIB``); ``None`` when the loaded library is the normal one.  Synchronises
+    the device.  ``{"failures": n, "code": ..., "what": ..., "line": ..., "value": ..., "limit": ...}``."""
+    out = (C.c_longlong * 4)()
+    status = load().b200_checked_build_report(out, (1 if clear else 0) | (2 if selftest else 0))
+    if status == ERR_UNSUPPORTED:
+        return None
+    check(status)
+    code, line = int(out[1]) >> 32, int(out[1]) & 0xFFFFFFFF
+    return {"failures": int(out[0]), "code": code, "what": CHECK_CODES.get(code, ""), "line": line,
+            "value": int(out[2]), "limit": int(out[3])}
 
 
 def device_count() -> int:

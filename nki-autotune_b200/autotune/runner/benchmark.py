@@ -23,6 +23,9 @@ from autotune.runner.types import CompileResult, OutputSpec, ProfileResult, capt
 TOL_BF16 = 1e-2   # max |a-e| / (|e| + rms(e)) for bf16 inputs, fp32 accumulation, bf16 output
 TOL_FP32 = 1e-5   # same metric for the fp32 configuration
 
+GUARD_BYTES = 16384       # canary band on either side of the output buffer (a multiple of 256: TMA stores stay aligned)
+GUARD_PATTERN = 0x5A      # every byte of both bands; checked after each candidate
+
 
 def generate_tensors(tensor_specs: dict[str, dict], seed: int) -> dict[str, np.ndarray]:
     """Seeded inputs: one ``default_rng(seed)``, tensors drawn in dict order.
@@ -70,6 +73,24 @@ def max_rel_err(actual, expected) -> float:
     return float(torch.max(torch.abs(a - e) / (torch.abs(e) + floor)))
 
 
+def guarded_output(M: int, N: int, dtype, device):
+    """(backing byte buffer, [M, N] view inside it): the output sits between two canary bands."""
+    import torch
+
+    nbytes = M * N * torch.empty((), dtype=dtype).element_size()
+    backing = torch.empty(GUARD_BYTES + nbytes + GUARD_BYTES, dtype=torch.uint8, device=device)
+    backing[:GUARD_BYTES].fill_(GUARD_PATTERN)
+    backing[GUARD_BYTES + nbytes:].fill_(GUARD_PATTERN)
+    return backing, backing[GUARD_BYTES:GUARD_BYTES + nbytes].view(dtype).view(M, N)
+
+
+def guards_intact(backing) -> bool:
+    """True when neither canary band around the output was written."""
+    lo = backing[:GUARD_BYTES]
+    hi = backing[backing.numel() - GUARD_BYTES:]
+    return bool((lo == GUARD_PATTERN).all()) and bool((hi == GUARD_PATTERN).all())
+
+
 class DeviceBatch:
     """Device-resident inputs, reference output and scratch shared by a batch of candidates."""
 
@@ -94,7 +115,8 @@ class DeviceBatch:
         else:
             self.M, self.K = self.a.shape
         self.N = self.b.shape[1]
-        self.out = torch.empty((self.M, self.N), dtype=self.a.dtype, device=device)
+        self.out_backing, self.out = guarded_output(self.M, self.N, self.a.dtype, device)
+        self.repeat = torch.empty_like(self.out)   # the previous launch's output, for the bit-identity check
         self.status = kernels.new_status(device)
         # larger than the 126 MB L2, overwritten between timed launches
         self.flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=device)
@@ -152,6 +174,22 @@ def benchmark_one(
         tol = TOL_FP32 if batch.is_fp32 else TOL_BF16
         if not (err <= tol):
             raise AssertionError(f"parity check failed: max-abs-rel error {err:.3e} > {tol:.0e}")
+        # Two cheap race detectors: one more launch must reproduce the output bit for bit (a
+        # barrier-phase slip or an unordered reduction shows up as run-to-run differences), and
+        # nothing may have been written outside the output buffer.
+        batch.repeat.copy_(batch.out)
+        if batch.is_fp32:
+            _time_fp32(batch, 0, 1)
+        else:
+            kernels.time_kernel(batch.family, batch.a, batch.b, batch.out, candidate.config, gamma=batch.gamma, eps=eps,
+                                warmup=0, iters=1, status=batch.status)
+        torch.cuda.synchronize()
+        if not torch.equal(batch.out.view(torch.uint8), batch.repeat.view(torch.uint8)):
+            raise AssertionError("output differs between two launches on the same inputs")
+        if not guards_intact(batch.out_backing):
+            batch.out_backing[:GUARD_BYTES].fill_(GUARD_PATTERN)
+            batch.out_backing[batch.out_backing.numel() - GUARD_BYTES:].fill_(GUARD_PATTERN)
+            raise AssertionError("bytes outside the output buffer were written")
         peaks = load_peaks()
         t = statistics.median(ms) * 1e-3
         flops, nbytes = algorithmic_work(batch.family, batch.M, batch.N, batch.K, batch.a.element_size())
@@ -168,6 +206,8 @@ def benchmark_one(
             "time_ms_min": float(min(ms)),
             "max_abs_rel_err": err,
             "tolerance": tol,
+            "repeat_bit_identical": True,
+            "guard_bands_intact": True,
             "config": dict(candidate.config),
             "peaks": peaks,
             "device": torch.cuda.get_device_name(torch.cuda.current_device()),

@@ -1080,6 +1080,48 @@ extern "C" int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, con
   return launch(pr, stream);
 }
 
+// ------------------------------------------------------------------- checked build
+#ifdef B200_CHECKED_BUILD
+// Hands the wrappers arguments their checks must refuse.  Every access below is skipped by its
+// check, so the kernel touches nothing: no tensor memory is allocated, the tensor map is never
+// read.  32 lanes x 3 refusals.
+__global__ void checked_selftest_kernel() {
+  using namespace b200;
+  st_shared_v4(cta_smem_bytes(), 0u, 0u, 0u, 0u);   // one byte past the shared window
+  uint32_t r[16];
+  tmem_ld_32x32b_x16(600u, r);                      // column 600 of 512
+  tma_store_2d(nullptr, 0u, -8, 0);                 // a store at a negative coordinate
+  if (r[0] != 0u) st_shared_v4(cta_smem_bytes(), r[0], 0u, 0u, 0u);  // keeps the load's result alive
+}
+#endif
+
+extern "C" int b200_checked_build_report(long long* out4, int flags) {
+  if (!out4) return set_error(B200_ERR_BAD_ARG, "checked_build_report: NULL pointer");
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+#ifdef B200_CHECKED_BUILD
+  if (flags & 2) {
+    checked_selftest_kernel<<<1, 32>>>();
+    int rc = check_cuda(cudaGetLastError(), "self-test launch");
+    if (rc) return rc;
+  }
+  int rc = check_cuda(cudaDeviceSynchronize(), "checked_build_report: synchronize");
+  if (rc) return rc;
+  unsigned long long log[4];
+  rc = check_cuda(cudaMemcpyFromSymbol(log, b200::g_check_log, sizeof log), "checked_build_report: read");
+  if (rc) return rc;
+  for (int i = 0; i < 4; ++i) out4[i] = static_cast<long long>(log[i]);
+  if (flags & 1) {
+    const unsigned long long zero[4] = {0, 0, 0, 0};
+    rc = check_cuda(cudaMemcpyToSymbol(b200::g_check_log, zero, sizeof zero), "checked_build_report: clear");
+    if (rc) return rc;
+  }
+  return B200_OK;
+#else
+  (void)flags;
+  return set_error(B200_ERR_UNSUPPORTED, "this library was built without -DB200_CHECKED_BUILD");
+#endif
+}
+
 #ifdef B200_MEASURE_HOOKS
 // measurement build only: copies the GEMM kernels' boundary stamps (g_gemm_trace) to the host
 extern "C" int b200_debug_gemm_trace(long long* host, size_t count) {

@@ -300,6 +300,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
   // store, so nothing serialises them.
   [[maybe_unused]] const int norm_pieces = p.K / 8;  // 16-byte pieces per row (K is a multiple of 64)
   auto norm_row = [&](int row) {
+    if (!B200_CHECK(row >= 0 && row < p.M, CHK_GLOBAL, row, p.M)) return;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     const uint4 ones = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);  // bf16 1.0 pairs
     const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<long long>(row) * p.K);
@@ -371,6 +372,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, mt, nt);
         const int m_base = (mt * CTA_GROUP + static_cast<int>(cta_rank)) * MC;
         const int n_base = nt * tile_n + static_cast<int>(cta_rank) * nc_sub;  // first UMMA's share; next at + umma_n
+        // a tile may hang over the edge of C (TMA fills and clips), but it starts inside it
+        if (!B200_CHECK(mt * CTA_GROUP * MC < p.M && nt * tile_n < p.N && kb0 < kb1 && kb1 <= num_k_blocks, CHK_SCHEDULE, tile, total_tiles)) break;
         // the loads of one stage
         auto arm_stage = [&](uint32_t s) {
           const uint32_t full_local = smem_u32(&ctrl->full[s]);
@@ -383,6 +386,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         auto load_a = [&](uint32_t s, int kb) {
           const uint32_t a_s = a_base + s * a_bytes;
           const int k0 = kb * tile_k;
+          if (!B200_CHECK(s < static_cast<uint32_t>(stages) && k0 < p.K, CHK_SCHEDULE, s, kb)) return;
           const uint32_t full_local = smem_u32(&ctrl->full[s]);
           if constexpr (PAIR) {
             const uint32_t full_leader = map_to_cta(full_local, 0);
@@ -406,6 +410,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
         auto load_b = [&](uint32_t s, int kb) {
           const uint32_t b_s = b_base + s * b_bytes;
           const int k0 = kb * tile_k;
+          if (!B200_CHECK(s < static_cast<uint32_t>(stages) && k0 < p.K, CHK_SCHEDULE, s, kb)) return;
           const uint32_t full_local = smem_u32(&ctrl->full[s]);
           // B chunks of 64 columns; after this CTA's share of one UMMA the column jumps to the next UMMA
           if constexpr (PAIR) {

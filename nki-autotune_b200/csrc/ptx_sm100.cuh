@@ -9,6 +9,66 @@
 namespace b200 {
 
 // ----------------------------------------------------------------------------------
+// Checked build (-DB200_CHECKED_BUILD): every wrapper below that takes a shared-memory address,
+// a tensor-memory address or TMA coordinates validates them first, and the kernels validate
+// their global indices with the same macro.  A failed check records the first offender
+// (code, source line, value, limit) in g_check_log, counts the rest, and the access is SKIPPED:
+// nothing traps and nothing out of range is touched (a skipped load leaves its consumer to its
+// bounded wait).  In the normal build B200_CHECK is the constant true and costs nothing.
+// ----------------------------------------------------------------------------------
+enum CheckCode : int {
+  CHK_SMEM_RANGE = 1,   // shared-memory access outside the CTA's window or misaligned
+  CHK_BARRIER = 2,      // mbarrier address outside the window or not 8-byte aligned
+  CHK_TMA_LOAD = 3,     // TMA load: destination outside the window / not 128-byte aligned, or x not 16-byte aligned
+  CHK_TMA_STORE = 4,    // TMA store: negative coordinate, x not 16-byte aligned, source outside the window
+  CHK_TMEM = 5,         // tensor-memory address beyond 512 columns / 128 lanes, or not this warp's lane quarter
+  CHK_GLOBAL = 6,       // global index beyond its extent
+  CHK_SCHEDULE = 7      // tile / k-block / stage / slot index beyond its extent
+};
+#ifdef B200_CHECKED_BUILD
+__device__ unsigned long long g_check_log[4];   // [0] failures  [1] code << 32 | line  [2] value  [3] limit
+__device__ __noinline__ bool check_failed(int code, int line, unsigned long long value, unsigned long long limit) {
+  if (atomicAdd(&g_check_log[0], 1ull) == 0ull) {
+    g_check_log[1] = (static_cast<unsigned long long>(code) << 32) | static_cast<unsigned>(line);
+    g_check_log[2] = value;
+    g_check_log[3] = limit;
+  }
+  return false;
+}
+#define B200_CHECK(ok, code, value, limit)                                                     \
+  ((ok) ? true                                                                                 \
+        : ::b200::check_failed((code), __LINE__, static_cast<unsigned long long>(value),        \
+                               static_cast<unsigned long long>(limit)))
+__device__ __forceinline__ uint32_t cta_smem_bytes() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%total_smem_size;" : "=r"(r));
+  return r;
+}
+// [addr, addr + bytes) inside this CTA's shared window and addr aligned to `align`.  In a cluster
+// launch a CTA's own shared addresses carry its rank above bit 24 (they are valid shared::cluster
+// addresses of itself), so the offset inside the window is the low 24 bits.
+__device__ __forceinline__ bool smem_ok(uint32_t addr, uint32_t bytes, uint32_t align, int code) {
+  const uint32_t window = cta_smem_bytes(), off = addr & 0x00FFFFFFu;
+  return B200_CHECK(addr % align == 0, code, addr, align) && B200_CHECK(off <= window && bytes <= window - off, code, addr, window);
+}
+// a tensor-memory address (lane << 16 | column) with `cols` columns behind it
+__device__ __forceinline__ bool tmem_ok(uint32_t taddr, uint32_t cols) {
+  return B200_CHECK((taddr & 0xFFFFu) + cols <= 512u, CHK_TMEM, taddr, cols) && B200_CHECK((taddr >> 16) < 128u, CHK_TMEM, taddr, 128u);
+}
+// tcgen05.ld / .st 32x32b: a warp reaches only the lane quarter 32 * (warp index % 4)
+__device__ __forceinline__ bool tmem_warp_ok(uint32_t taddr, uint32_t cols) {
+  return tmem_ok(taddr, cols) && B200_CHECK((taddr >> 16) == 32u * ((threadIdx.x >> 5) & 3u), CHK_TMEM, taddr, threadIdx.x >> 5);
+}
+__device__ __forceinline__ uint32_t cta_smem_bytes_or_max() { return cta_smem_bytes(); }
+#else
+#define B200_CHECK(ok, code, value, limit) (true)
+__device__ __forceinline__ uint32_t cta_smem_bytes_or_max() { return 0xFFFFFFFFu; }
+__device__ __forceinline__ bool smem_ok(uint32_t, uint32_t, uint32_t, int) { return true; }
+__device__ __forceinline__ bool tmem_ok(uint32_t, uint32_t) { return true; }
+__device__ __forceinline__ bool tmem_warp_ok(uint32_t, uint32_t) { return true; }
+#endif
+
+// ----------------------------------------------------------------------------------
 // addresses
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -63,16 +123,19 @@ __device__ __forceinline__ bool elect_one() {
 // mbarrier
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return;
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return;
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return;
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // arrive on a barrier that lives in another CTA of the cluster (address from map_to_cta)
@@ -91,6 +154,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 }
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return false;
   uint32_t ok;
   asm volatile(
       "{\n\t"
@@ -106,6 +170,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // cluster-scope acquire: pairs with remote arrivals (mbar_arrive_cluster) and with
 // tcgen05.commit / TMA completions issued by the peer CTA
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return false;
   uint32_t ok;
   asm volatile(
       "{\n\t"
@@ -132,14 +197,17 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   return v;
 }
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  if (!smem_ok(addr, 16, 16, CHK_SMEM_RANGE)) return make_uint4(0, 0, 0, 0);
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  if (!smem_ok(addr, 16, 16, CHK_SMEM_RANGE)) return;
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  if (!smem_ok(addr, 16, 16, CHK_SMEM_RANGE)) return;
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
@@ -158,6 +226,7 @@ __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
 // 2-D tile load into this CTA's shared memory, completion on this CTA's mbarrier
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
                                             int c1) {
+  if (!smem_ok(dst, 128, 128, CHK_TMA_LOAD) || !B200_CHECK((c0 & 7) == 0, CHK_TMA_LOAD, c0, 8)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
@@ -169,6 +238,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
 // completes on `cluster_bar`, which may be the pair leader's mbarrier (map_to_cta address)
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
                                                  uint32_t cluster_bar, int c0, int c1) {
+  if (!smem_ok(dst, 128, 128, CHK_TMA_LOAD) || !B200_CHECK((c0 & 7) == 0, CHK_TMA_LOAD, c0, 8)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];"
@@ -180,6 +250,7 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap,
 // one elected lane performs the operation (see umma_bf16_elect for why the loop stays uniform).
 __device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const void* tmap, uint32_t bar, int c0,
                                                   int c1) {
+  if (!smem_ok(dst, 128, 128, CHK_TMA_LOAD) || !B200_CHECK((c0 & 7) == 0, CHK_TMA_LOAD, c0, 8)) return;
   asm volatile(
       "{\n\t"
       ".reg .pred q;\n\t"
@@ -193,6 +264,7 @@ __device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const void* tmap
 }
 __device__ __forceinline__ void tma_load_2d_pair_elect(uint32_t dst, const void* tmap,
                                                        uint32_t cluster_bar, int c0, int c1) {
+  if (!smem_ok(dst, 128, 128, CHK_TMA_LOAD) || !B200_CHECK((c0 & 7) == 0, CHK_TMA_LOAD, c0, 8)) return;
   asm volatile(
       "{\n\t"
       ".reg .pred q;\n\t"
@@ -205,6 +277,7 @@ __device__ __forceinline__ void tma_load_2d_pair_elect(uint32_t dst, const void*
       : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint32_t bar, uint32_t bytes) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return;
   asm volatile(
       "{\n\t"
       ".reg .pred q;\n\t"
@@ -215,6 +288,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint32_t bar, uint32
       : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_elect(uint32_t bar) {
+  if (!smem_ok(bar, 8, 8, CHK_BARRIER)) return;
   asm volatile(
       "{\n\t"
       ".reg .pred q;\n\t"
@@ -225,6 +299,7 @@ __device__ __forceinline__ void mbar_arrive_elect(uint32_t bar) {
 }
 // 2-D tile store shared -> global (bulk async group)
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int c0, int c1) {
+  if (!smem_ok(src, 128, 128, CHK_TMA_STORE) || !B200_CHECK(c0 >= 0 && c1 >= 0 && (c0 & 3) == 0, CHK_TMA_STORE, c0, c1)) return;
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                :
                : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1)
@@ -279,6 +354,7 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                           uint32_t idesc, uint32_t accumulate) {
+  if (!tmem_ok(tmem_d, 1) || !B200_CHECK(((adesc & 0x3FFFull) << 4) < cta_smem_bytes_or_max(), CHK_SMEM_RANGE, adesc, 0) || !B200_CHECK(((bdesc & 0x3FFFull) << 4) < cta_smem_bytes_or_max(), CHK_SMEM_RANGE, bdesc, 0)) return;
   if constexpr (CTA_GROUP == 1)
     asm volatile(
         "{\n\t"
@@ -309,6 +385,7 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_bf16_elect(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                                 uint32_t idesc, uint32_t accumulate) {
+  if (!tmem_ok(tmem_d, 1) || !B200_CHECK(((adesc & 0x3FFFull) << 4) < cta_smem_bytes_or_max(), CHK_SMEM_RANGE, adesc, 0) || !B200_CHECK(((bdesc & 0x3FFFull) << 4) < cta_smem_bytes_or_max(), CHK_SMEM_RANGE, bdesc, 0)) return;
   if constexpr (CTA_GROUP == 1)
     asm volatile(
         "{\n\t"
@@ -338,6 +415,7 @@ __device__ __forceinline__ void umma_bf16_elect(uint32_t tmem_d, uint64_t adesc,
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
                                              uint32_t idesc, uint32_t accumulate) {
+  if (!tmem_ok(tmem_d, 1) || !tmem_ok(tmem_a, 1) || !B200_CHECK(((bdesc & 0x3FFFull) << 4) < cta_smem_bytes_or_max(), CHK_SMEM_RANGE, bdesc, 0)) return;
   if constexpr (CTA_GROUP == 1)
     asm volatile(
         "{\n\t"
@@ -364,6 +442,7 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
 template <int CTA_GROUP>
 __device__ __forceinline__ void umma_bf16_ts_elect(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
                                                    uint32_t idesc, uint32_t accumulate) {
+  if (!tmem_ok(tmem_d, 1) || !tmem_ok(tmem_a, 1) || !B200_CHECK(((bdesc & 0x3FFFull) << 4) < cta_smem_bytes_or_max(), CHK_SMEM_RANGE, bdesc, 0)) return;
   if constexpr (CTA_GROUP == 1)
     asm volatile(
         "{\n\t"
@@ -390,6 +469,7 @@ __device__ __forceinline__ void umma_bf16_ts_elect(uint32_t tmem_d, uint32_t tme
 
 // registers -> tensor memory: lane i of the warp writes TMEM lane (base lane + i), 16 columns
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  if (!tmem_warp_ok(taddr, 16)) return;
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -442,6 +522,11 @@ __device__ __forceinline__ void umma_commit_pair_elect(uint32_t bar, uint16_t ct
 // tensor memory -> registers: lane i of the warp reads TMEM lane (base lane + i),
 // N consecutive 32-bit columns
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  if (!tmem_warp_ok(taddr, 32)) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = 0u;
+    return;
+  }
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -455,6 +540,11 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  if (!tmem_warp_ok(taddr, 16)) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = 0u;
+    return;
+  }
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"

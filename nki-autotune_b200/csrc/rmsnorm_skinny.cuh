@@ -280,6 +280,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
           const uint32_t w_s = w_base + ring.s * w_bytes;
           const uint32_t fw = smem_u32(&ctrl->full_w[ring.s]);
           const int k0 = work.kb_at(i) * tile_k;
+          if (!B200_CHECK(k0 >= 0 && k0 < p.K && work.n0 >= 0 && work.n0 < p.N, CHK_SCHEDULE, k0, work.n0)) { ok = false; break; }
           mbar_arrive_expect_tx_elect(fw, seg_bytes);
           for (int c = 0; c < chunks; ++c)
             tma_load_2d_elect(w_s + c * tile_k * 128, &tm_w, fw, work.n0 + 64 * c, k0);
@@ -434,6 +435,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
           for (int j = 0; j < 2; ++j) v[r][j] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int d = d_lo; d <= d_hi; ++d) {
           if (V * d / p.donors == V * (d + 1) / p.donors) continue;  // a donor without units
+          if (!B200_CHECK(d >= 0 && d < p.donors && nt < (p.N + 255) / 256, CHK_GLOBAL, d, nt)) continue;
           const float* other = p.partial + static_cast<size_t>(d + nt) * SKINNY_SLOT_FLOATS;
           float4 t[4][2];  // 8 independent 16-byte loads in flight per lane
 #pragma unroll
@@ -499,6 +501,7 @@ rmsnorm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const SkinnyPara
       if (kind == SK_DONATE) {
         // publish the partial tile (slot index = donor index + tile index, unique along the chain of
         // donated ranges), then add the k-blocks to the tile's counter
+        if (!B200_CHECK(static_cast<int>(blockIdx.x) < p.donors && nt < (p.N + 255) / 256, CHK_GLOBAL, blockIdx.x, nt)) break;
         float* const slot = p.partial + static_cast<size_t>(blockIdx.x + nt) * SKINNY_SLOT_FLOATS;
 #pragma unroll
         for (int r = 0; r < 4; ++r)

@@ -38,6 +38,22 @@ def native_lib():
 
 
 @pytest.fixture(scope="session")
+def checked_lib_path(native_lib):
+    """Path of the checked variant of the library (``-DB200_CHECKED_BUILD``), built like the normal one."""
+    import importlib.util
+    import shutil
+
+    have_nvcc = shutil.which("nvcc") is not None or Path("/usr/local/cuda/bin/nvcc").is_file()
+    spec = importlib.util.spec_from_file_location("b200_build", PKG / "build.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    if have_nvcc:
+        mod.build(checked=True)
+    assert mod.CHECKED_LIB_PATH.exists(), "build it with: python nki-autotune_b200/build.py --checked"
+    return mod.CHECKED_LIB_PATH
+
+
+@pytest.fixture(scope="session")
 def golden():
     import numpy as np
 

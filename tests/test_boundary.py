@@ -120,6 +120,21 @@ def test_library_exports_every_declared_symbol(native_lib):
     assert native_lib.b200_abi_version() == 1
 
 
+def test_checked_variant_exports_the_same_symbols_and_normal_one_reports_none(native_lib, checked_lib_path):
+    """The checked library is a drop-in (selected with B200_AUTOTUNE_LIB); the normal one answers
+    that it has no device-side check record."""
+    import ctypes as C
+
+    from autotune import native
+
+    checked = C.CDLL(str(checked_lib_path))
+    for name in native.SIGNATURES:
+        assert hasattr(checked, name), name
+    assert checked.b200_abi_version() == 1
+    out = (C.c_longlong * 4)(7, 7, 7, 7)
+    assert native_lib.b200_checked_build_report(out, 0) == native.ERR_UNSUPPORTED and list(out) == [0, 0, 0, 0]
+
+
 def test_cfg_check_budgets(native_lib):
     from autotune import native
 
@@ -315,3 +330,21 @@ def test_cyclic_rows_cover_c_once():
         assert len({b - a for a, b in pieces}) == 1 and (pieces[0][1] - pieces[0][0]) % 8 == 0
     with pytest.raises(ValueError):
         cyclic_rows(1000, 0, 3, 2)
+
+
+def test_guard_bands_notice_a_stray_write():
+    """The output of a candidate sits between two canary bands (host logic, CPU tensors)."""
+    import torch
+
+    from autotune.runner import benchmark as B
+
+    backing, out = B.guarded_output(5, 7, torch.bfloat16, "cpu")
+    assert out.shape == (5, 7) and out.dtype == torch.bfloat16
+    assert out.data_ptr() - backing.data_ptr() == B.GUARD_BYTES and B.GUARD_BYTES % 256 == 0
+    out.fill_(3.0)
+    assert B.guards_intact(backing)
+    backing[B.GUARD_BYTES + 5 * 7 * 2] = 0           # first byte after the output
+    assert not B.guards_intact(backing)
+    backing[B.GUARD_BYTES + 5 * 7 * 2] = B.GUARD_PATTERN
+    backing[B.GUARD_BYTES - 1] = 0                   # last byte before it
+    assert not B.guards_intact(backing)

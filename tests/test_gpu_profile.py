@@ -35,6 +35,7 @@ def test_profile_sweep_writes_reference_cache_layout(native_lib, tmp_path):
     assert (tmp_path / ok / f"{ok}.py").exists() and (tmp_path / ok / "log-neuron-cc.txt").exists()
     summary = json.loads((tmp_path / ok / "profile_summary.json").read_text())
     assert summary["max_abs_rel_err"] <= 1e-2 and summary["total_time"] > 0
+    assert summary["repeat_bit_identical"] and summary["guard_bands_intact"]
     detail = json.loads((tmp_path / ok / "profile.json").read_text())    # detailed run: plan + kernel's own cycle count
     assert detail["plan"]["kernel"].startswith("gemm_tcgen05_kernel") and detail["plan"]["registers"] > 0
     assert detail["cta_lifetime_sm_cycles"] > 0 and 0 < detail["tensor_pipe_busy_estimate"] <= 1.0
