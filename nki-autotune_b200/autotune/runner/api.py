@@ -32,6 +32,7 @@ def profile(
     shard: tuple[int, int] | None = None,
     retime_top: int = 0,
     inputs: dict | None = None,
+    keep_workers: bool = False,
 ) -> ProfileOutput:
     """Validate and time a set of candidates on the GPUs of this box.
 
@@ -53,6 +54,10 @@ def profile(
             candidates again on one GPU so that the leaders are ranked on one device (extension).
         inputs: Input arrays by tensor name, if the caller already holds what ``seed`` and the
             specs would generate; nothing is generated then (extension).
+        keep_workers: The per-GPU worker processes of a multi-GPU sweep stay alive, pinned to their
+            GPUs with their CUDA contexts, for the next ``profile()`` call of this process;
+            ``autotune.runner.driver.shutdown_workers()`` (or the end of the process) ends them
+            (extension).
 
     Returns:
         ``ProfileOutput`` with every candidate present, as a success or as a failure row.
@@ -77,6 +82,7 @@ def profile(
         shard=shard,
         retime_top=retime_top,
         inputs=inputs,
+        keep_workers=keep_workers,
     )
     elapsed_s = time.monotonic() - start
     logger.info("Profile complete: %d results in %.1fs", len(results), elapsed_s)

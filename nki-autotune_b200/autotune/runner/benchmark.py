@@ -104,7 +104,6 @@ class DeviceBatch:
         self.device = device
         self.scalars = dict(scalars)
         names = list(kwargs)
-        self.host = kwargs
         self.tensors = {n: kernels.to_device(np.asarray(v), device) for n, v in kwargs.items()}
         self.a = self.tensors[names[0]]
         self.b = self.tensors[names[-1]]

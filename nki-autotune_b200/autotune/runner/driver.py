@@ -12,6 +12,7 @@ it was on: that candidate becomes a failure row and a fresh worker takes over th
 
 from __future__ import annotations
 
+import atexit
 import logging
 import multiprocessing as mp
 import os
@@ -163,9 +164,12 @@ def gpu_shard_worker(items: list[dict], opts: dict, emit: Callable[[ProfileResul
                     kwargs = generate_tensors(kd["tensor_specs"], opts["seed"])
                 out = OutputSpec(_OUTPUT_TENSOR_NAME, kd["output_shape"], resolve_dtype(kd["input_dtype_name"]))
                 batches[key] = DeviceBatch(kd["func_name"], kwargs, out, cand.scalars)
-                del kwargs
+                del kwargs  # (DeviceBatch keeps no reference to the host arrays)
                 for h in handles:  # the device copy exists: the mapping can go
-                    h.close()
+                    try:
+                        h.close()
+                    except BufferError:  # a view of the block is still alive somewhere: leave it mapped
+                        logger.warning("shared input block %s stays mapped in worker %d", h.name, os.getpid())
             result = benchmark_one(
                 batches[key], cr, cand, warmup=opts["warmup"], iters=opts["iters"],
                 collect_detailed_profile=opts["detailed"],
@@ -192,6 +196,59 @@ def _child_main(worker_fn, items, opts, device_env, conn) -> None:
         conn.close()
 
 
+def _service_main(device_env, conn) -> None:
+    """Entry point of a resident worker: pins the GPU, then serves jobs until told to stop (or
+    until the parent's end of the pipe closes).  One job = one shard of one ``profile()`` call."""
+    if device_env is not None:
+        os.environ["CUDA_VISIBLE_DEVICES"] = device_env
+    try:
+        while True:
+            try:
+                msg = conn.recv()
+            except (EOFError, OSError):
+                return
+            if msg[0] != "job":
+                return
+            _, worker_fn, items, opts = msg
+            try:
+                worker_fn(items, opts, lambda r: conn.send(("result", tuple(r))))
+                conn.send(("done", None))
+            except BaseException as exc:  # noqa: BLE001
+                conn.send(("crash", capture_error(exc)))
+                return  # a worker that crashed is not reused
+    finally:
+        conn.close()
+
+
+# Resident workers, by the device they are pinned to: processes that finished a shard cleanly and
+# wait for the next profile() call of this process (keep_workers=True).  A second sweep then pays
+# neither the process start nor the CUDA context again.
+_RESIDENT: dict[str | None, tuple] = {}
+
+
+def shutdown_workers() -> None:
+    """Stop every resident worker of this process (also runs at interpreter exit)."""
+    for key in list(_RESIDENT):
+        proc, conn = _RESIDENT.pop(key)
+        try:
+            conn.send(("stop",))
+        except (OSError, ValueError, BrokenPipeError):
+            pass
+        proc.join(timeout=10)
+        if proc.is_alive():
+            proc.terminate()  # exactly the PID this pool started
+            proc.join(timeout=10)
+        conn.close()
+
+
+atexit.register(shutdown_workers)
+
+
+def resident_worker_pids() -> dict:
+    """{device: pid} of the workers that are waiting for a next sweep."""
+    return {key: proc.pid for key, (proc, _) in _RESIDENT.items() if proc.is_alive()}
+
+
 def run_sharded(
     shards: list[list[dict]],
     worker_fn: Callable,
@@ -199,12 +256,17 @@ def run_sharded(
     device_envs: list[str | None],
     deadline_s: float = DEFAULT_DEADLINE_S,
     startup_s: float = 600.0,
+    keep_workers: bool = False,
 ) -> list[ProfileResult]:
     """Run one worker process per shard and gather ``ProfileResult`` rows on the host.
 
     Each item must carry ``"kernel_name"``.  ``worker_fn(items, opts, emit)`` must call
     ``emit`` once per item, in order.  The first result of a worker may take ``startup_s``
     (process start, CUDA context, input generation); every later one ``deadline_s``.
+
+    ``keep_workers``: a worker that finishes its shard cleanly stays alive, pinned to its GPU,
+    and serves the matching shard of the next call (``shutdown_workers()`` ends them; so does the
+    end of this process).  Workers that crash or overrun a deadline are always replaced.
     """
     ctx = mp.get_context("spawn")
     results: list[ProfileResult] = []
@@ -219,16 +281,37 @@ def run_sharded(
             self.fresh = True
 
         def start(self) -> None:
-            parent, child = ctx.Pipe(duplex=False)
-            self.proc = ctx.Process(
-                target=_child_main, args=(worker_fn, list(self.pending), opts, device_envs[self.idx], child),
-                daemon=True,
-            )
-            self.proc.start()
-            child.close()
-            self.conn = parent
+            key = device_envs[self.idx]
+            if keep_workers:
+                resident = _RESIDENT.pop(key, None)
+                if resident is not None and not resident[0].is_alive():
+                    resident[1].close()
+                    resident = None
+                if resident is None:
+                    parent, child = ctx.Pipe(duplex=True)
+                    proc = ctx.Process(target=_service_main, args=(key, child), daemon=True)
+                    proc.start()
+                    child.close()
+                    resident = (proc, parent)
+                self.proc, self.conn = resident
+                self.conn.send(("job", worker_fn, list(self.pending), opts))
+            else:
+                parent, child = ctx.Pipe(duplex=False)
+                self.proc = ctx.Process(
+                    target=_child_main, args=(worker_fn, list(self.pending), opts, key, child),
+                    daemon=True,
+                )
+                self.proc.start()
+                child.close()
+                self.conn = parent
             self.fresh = True
             self.deadline = time.monotonic() + startup_s
+
+        def park(self) -> None:
+            """The shard is done and the worker is healthy: keep it for the next call."""
+            _RESIDENT[device_envs[self.idx]] = (self.proc, self.conn)
+            self.proc = None
+            self.conn = None
 
         def stop(self) -> None:
             if self.proc is not None:
@@ -281,7 +364,10 @@ def run_sharded(
                     for item in slot.pending:
                         results.append(make_failure(item["kernel_name"], "worker finished without a result"))
                     slot.pending = []
-                    slot.stop()
+                    if keep_workers and device_envs[slot.idx] not in _RESIDENT:
+                        slot.park()
+                    else:
+                        slot.stop()
                 elif kind == "crash":
                     _fail_current(slot, f"worker crashed:\n{payload}")
                 else:
@@ -296,6 +382,13 @@ def run_sharded(
                 _fail_current(slot, f"worker exceeded its {limit:.0f} s deadline and was stopped")
                 progressed = True
             if not slot.pending:
+                if keep_workers and slot.proc is not None and device_envs[slot.idx] not in _RESIDENT:
+                    # every row is in; the worker's own "done" follows at once -- park it when it does
+                    try:
+                        if slot.conn.poll(5.0) and slot.conn.recv()[0] == "done":
+                            slot.park()
+                    except (EOFError, OSError):
+                        pass
                 slot.stop()
                 active.remove(slot)
         if not progressed:
@@ -389,8 +482,12 @@ def run_pipeline(
     shard: tuple[int, int] | None = None,
     retime_top: int = 0,
     inputs: dict | None = None,
+    keep_workers: bool = False,
 ) -> tuple[list[ProfileResult], dict[str, str]]:
     """Validate + time every candidate; returns ``(results, compiler_logs)``.
+
+    ``keep_workers``: the per-GPU worker processes of the sweep stay alive for the next call of
+    this process (see ``run_sharded``); the sweep then runs in worker processes even on one GPU.
 
     ``inputs``: input arrays by tensor name that the caller already holds (they must be what the
     seed and specs would give); the sweep then generates nothing.  Without it the tensors are
@@ -457,7 +554,7 @@ def run_pipeline(
                 compile_errors = []
             n_use = 1
         if accepted:
-            if n_use <= 1:
+            if n_use <= 1 and not (keep_workers and shard is None):
                 gpu_shard_worker(accepted, opts, hw_results.append)
             else:
                 shared = SharedInputs()
@@ -466,7 +563,7 @@ def run_pipeline(
                     opts["inputs"] = None  # the arrays travel as shared-memory names, not through pickles
                     shards = shard_round_robin(accepted, n_use)
                     devices = _visible_devices(n_use)
-                    hw_results = run_sharded(shards, gpu_shard_worker, opts, devices, deadline_s)
+                    hw_results = run_sharded(shards, gpu_shard_worker, opts, devices, deadline_s, keep_workers=keep_workers)
                     if retime_top > 0:
                         hw_results = retime_top_k(hw_results, accepted, retime_top, opts, devices[0], deadline_s)
                 finally:

@@ -241,3 +241,40 @@ def test_row_split_replicates_and_gathers_gloo(tmp_path, world, port):
         assert res["64"][:3] == [True, True, True] and res["64"][3] == [64, 16]
         assert res["1000"][:3] == [True, True, True] and res["1000"][3] == [1000, 16]
         assert res["cyclic"] == [True, True, True, True]
+
+
+def test_resident_workers_serve_the_next_sweep_and_failed_ones_are_replaced():
+    """keep_workers: the second call is served by the processes of the first (same PIDs, still pinned
+    to their devices); a worker that crashes or hangs is replaced, never parked; shutdown ends them."""
+    from autotune.runner import driver
+
+    driver.shutdown_workers()
+    items = [{"kernel_name": f"k_{i}.py", "i": i} for i in range(6)]
+    shards = shard_round_robin(items, 2)
+    try:
+        first = run_sharded(shards, fake_workers.well_behaved, {}, ["0", "1"], deadline_s=30, startup_s=60, keep_workers=True)
+        pids_1 = {r.profiler_summary["device_env"]: r.profiler_summary["pid"] for r in first}
+        assert driver.resident_worker_pids() == pids_1 and len(pids_1) == 2
+        second = run_sharded(shards, fake_workers.well_behaved, {}, ["0", "1"], deadline_s=30, startup_s=60, keep_workers=True)
+        assert {r.profiler_summary["device_env"]: r.profiler_summary["pid"] for r in second} == pids_1
+        assert sorted(r.kernel_name for r in second) == sorted(it["kernel_name"] for it in items)
+        # a job that crashes on device "0" and hangs on device "1": both workers are replaced, the
+        # remaining candidates of each shard still get their rows, and only healthy workers are parked
+        bad = [dict(items[0], inject="raise"), dict(items[1], inject="hang")] + items[2:]
+        third = run_sharded(shard_round_robin(bad, 2), fake_workers.faulty, {}, ["0", "1"], deadline_s=2.0, startup_s=20.0,
+                            keep_workers=True)
+        by_name = {r.kernel_name: r for r in third}
+        assert "injected failure" in by_name["k_0.py"].hardware_output and "deadline" in by_name["k_1.py"].hardware_output
+        assert all(by_name[f"k_{i}.py"].profiler_summary is not None for i in range(2, 6))
+        pids_3 = driver.resident_worker_pids()
+        assert set(pids_3) == {"0", "1"} and not (set(pids_3.values()) & set(pids_1.values()))
+        # without keep_workers nothing is parked or taken from the pool
+        fourth = run_sharded(shards, fake_workers.well_behaved, {}, ["0", "1"], deadline_s=30, startup_s=60)
+        assert not ({r.profiler_summary["pid"] for r in fourth} & set(pids_3.values()))
+        assert driver.resident_worker_pids() == pids_3
+    finally:
+        driver.shutdown_workers()
+    assert driver.resident_worker_pids() == {}
+    for pid in list(pids_1.values()) + list(pids_3.values()):
+        with pytest.raises(OSError):
+            os.kill(pid, 0)          # gone (signal 0 only probes)

@@ -127,3 +127,34 @@ def test_candidate_whose_wait_runs_out_does_not_poison_the_next_one(native_lib):
     assert len(bufs) == 1
     counters = bufs[0][-256:]  # next row to claim, departed CTAs, rows ready per 128-row block
     assert int((counters != 0).sum()) == 0
+
+
+def test_resident_worker_serves_two_sweeps_on_the_gpu(native_lib):
+    """keep_workers: the sweep runs in a worker process (also on one GPU); the process, with its CUDA
+    context, serves the next profile() call, which therefore starts faster, and both give the same
+    rows; shutdown_workers() ends it."""
+    import time
+
+    from autotune.runner import driver
+    from autotune.runner.api import profile
+    from autotune.runner.candidate import enumerate_grid, jobs_from_candidates
+
+    driver.shutdown_workers()
+    k = m = n = 1024
+    s = {"kind": "normal", "scale": k ** -0.5}
+    cands = enumerate_grid("matmul_lhsT_rhs", tile_m=(128, 256), tile_n=(128, 256), tile_k=(64,), stages=(3,), cluster_m=(1,))
+    jobs = jobs_from_candidates(cands, (m, n), {"lhs_T": ((k, m), "bfloat16", s), "rhs": ((k, n), "bfloat16", s)})
+    try:
+        t0 = time.monotonic()
+        first = profile(jobs, "", 3, "b200", False, warmup=2, iters=5, n_gpus=1, keep_workers=True)
+        t1 = time.monotonic()
+        pids = driver.resident_worker_pids()
+        assert len(pids) == 1 and len(first.successes) == len(jobs) and not first.failures
+        second = profile(jobs, "", 3, "b200", False, warmup=2, iters=5, n_gpus=1, keep_workers=True)
+        t2 = time.monotonic()
+        assert driver.resident_worker_pids() == pids
+        assert [r.kernel_name for r in second.successes] == [r.kernel_name for r in first.successes]
+        assert (t2 - t1) < (t1 - t0), (t1 - t0, t2 - t1)   # no process start, no CUDA context, no module load
+    finally:
+        driver.shutdown_workers()
+    assert driver.resident_worker_pids() == {}
