@@ -558,21 +558,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a,
             if (n_sub == 1) issue_k_block(std::integral_constant<int, 1>{}, half_const);
             else issue_k_block(std::integral_constant<int, 2>{}, half_const);
           };
-          if (halves && (kb == kb0 || kb == kb1 - 1)) {
-            // first and / or last k-block of the tile: half by half
+          if (halves) {
+            // Half by half in every k-block, so that the first and last k-block of a tile -- which hand
+            // the halves over separately -- run the same instructions as all the others (a path taken
+            // once per tile would be fetched cold every time)
+            issue(std::integral_constant<int, 0>{});
+            if (kb == kb1 - 1) commit_to(&ctrl->acc_full[0]);
             if (kb == kb0) {  // (half 0 was waited for above)
-              issue(std::integral_constant<int, 0>{});
-              if (kb == kb1 - 1) commit_to(&ctrl->acc_full[0]);
               ok = bounded_wait<false>(wctx, smem_u32(&ctrl->acc_empty[1]), acc.ph ^ 1u, 201, tile, -1);
               ok = __all_sync(0xffffffffu, ok);
               if (!ok) break;
               tc_fence_after();
-              issue(std::integral_constant<int, 1>{});
-            } else {
-              issue(std::integral_constant<int, 0>{});
-              commit_to(&ctrl->acc_full[0]);
-              issue(std::integral_constant<int, 1>{});
             }
+            issue(std::integral_constant<int, 1>{});
           } else {
             issue(std::integral_constant<int, -1>{});
           }
