@@ -1,12 +1,14 @@
 """The large-M product split by rows of C over the GPUs of one box.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        examples/row_split_large_m.py [--m 131072] [--overlap]
+        examples/row_split_large_m.py [--m 131072] [--overlap] [--peer-stores]
 
 C[M, 4096] = lhsT[4096, M]^T . rhs[4096, 4096] with M = 131072 (seed 4, N(0,1)/sqrt(K), bf16): rank r
 multiplies its share of the columns of lhsT by the whole of rhs.  rhs is uploaded by rank 0 only and
 replicated over NVLink; C is all-gathered on the device into every GPU's memory (``--overlap``: the
-block-cyclic split, where the all-gather of one band runs beside the GEMM of the next).  Rank 0
+block-cyclic split, where the all-gather of one band runs beside the GEMM of the next;
+``--peer-stores``: the same split with the library's own exchange, a kernel that stores each band's
+rows into the other GPUs' copies of C over NVLink, in place of the collective).  Rank 0
 then gathers nothing more: every rank checks rows of ITS copy of C against a host product of the same
 inputs (fp32 BLAS on the bf16-rounded values) and the ranks' verdicts are
 collected on the host.  The reference has no multi-device path (its benchmark loop is one device:
@@ -33,6 +35,7 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=131072)
     ap.add_argument("--overlap", action="store_true")
     ap.add_argument("--chunks", type=int, default=8)
+    ap.add_argument("--peer-stores", action="store_true")
     args = ap.parse_args()
 
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -45,7 +48,7 @@ def main() -> None:
     # every rank draws the same seeded tensors (the recipe of the benchmark configuration) and keeps its share
     t = generate_tensors({"lhs_T": {"shape": [K, M], "dtype": "bfloat16", "dist": d},
                           "rhs": {"shape": [K, N], "dtype": "bfloat16", "dist": d}}, seed=4)
-    chunks = args.chunks if args.overlap else 1
+    chunks = args.chunks if (args.overlap or args.peer_stores) else 1
     if chunks > 1:
         pieces = sharded.cyclic_rows(M, rank, world, chunks)
     else:
@@ -53,8 +56,9 @@ def main() -> None:
     mine = np.concatenate([t["lhs_T"][:, p0:p1] for p0, p1 in pieces], axis=1)
     lhs_T_block = kernels.to_device(mine)
     rhs = sharded.replicate(kernels.to_device(t["rhs"]) if rank == 0 else None, (K, N), torch.bfloat16, "cuda", src=0)
-    full = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-    run = lambda: sharded.matmul_lhsT_rhs_row_split(lhs_T_block, rhs, M, out_full=full, chunks=chunks)  # noqa: E731
+    peers = sharded.PeerCopies(M, N) if args.peer_stores else None
+    full = peers.local if peers is not None else torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    run = lambda: sharded.matmul_lhsT_rhs_row_split(lhs_T_block, rhs, M, out_full=full, chunks=chunks, peers=peers)  # noqa: E731
     for _ in range(2):
         run()
     torch.cuda.synchronize()
@@ -76,9 +80,12 @@ def main() -> None:
     dist.all_gather_object(errs, err)
     if rank == 0:
         flops = 2.0 * M * N * K
-        print(f"[row split] M={M} over {world} GPUs{' (overlapped all-gather)' if chunks > 1 else ''}: {float(ms):.3f} ms per product "
-              f"including the all-gather = {flops / float(ms) / 1e9:.0f} TFLOP/s aggregate")
+        how = " (peer stores beside the GEMM)" if peers is not None else (" (overlapped all-gather)" if chunks > 1 else "")
+        print(f"[row split] M={M} over {world} GPUs{how}: {float(ms):.3f} ms per product "
+              f"including the exchange = {flops / float(ms) / 1e9:.0f} TFLOP/s aggregate")
         print(f"[row split] max-abs-rel error of 64 rows of every rank's gathered copy: {['%.2e' % e for e in errs]} (tolerance 1e-2)")
+    if peers is not None:
+        peers.close()
     dist.destroy_process_group()
 
 

@@ -93,6 +93,24 @@ int b200_device_count(int* count);
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
                    long* smem_bytes, int* tmem_cols);
 
+/* Exchange step of the large-M row split (no counterpart upstream, which gathers on the host,
+ * autotune/src/autotune/runner/driver.py:97 being one device): copies `bytes` bytes from src (this
+ * GPU's memory) to each of the n_peers (<= 8) destinations, which are pointers into OTHER GPUs'
+ * memory mapped into this process (CUDA IPC or any other peer mapping; peer access enabled), with
+ * plain 16-byte stores over NVLink.  The kernel reads local memory only and waits for nothing;
+ * the data is in place when the kernel has completed, so the ranks need a stream-ordered barrier
+ * of their own before they read what the others pushed.  max_ctas > 0 caps the grid (to run beside
+ * a GEMM).  src, every destination and bytes must be multiples of 16. */
+int b200_peer_store(const void* src, void* const* peer_dst, int n_peers, size_t bytes, int max_ctas, void* stream);
+
+/* Maps memory that another process of this node exported (cudaIpcGetMemHandle: 64 bytes) into the
+ * address space of the CURRENT device and returns the base of the exported allocation; peer access
+ * from the current device to the owner's is turned on if they differ.  The destinations of
+ * b200_peer_store must be mapped this way (under the GPU that will run the kernel).
+ * b200_ipc_close unmaps. */
+int b200_ipc_open(const void* handle64, void** base);
+int b200_ipc_close(void* base);
+
 /* The checked build (libb200_autotune_checked.so, compiled with -DB200_CHECKED_BUILD; the same
  * entry points, for debugging, several times slower): every shared-memory, tensor-memory and
  * barrier address, every TMA coordinate and the kernels' global and schedule indices are

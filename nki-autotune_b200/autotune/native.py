@@ -87,6 +87,9 @@ SIGNATURES = {
     ),
     "b200_describe_launch": (C.c_int, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long, C.c_char_p, C.c_size_t]),
     "b200_checked_build_report": (C.c_int, [C.POINTER(C.c_longlong), C.c_int]),
+    "b200_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "b200_ipc_close": (C.c_int, [C.c_void_p]),
+    "b200_peer_store": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_size_t, C.c_int, C.c_void_p]),
     "b200_default_cfg": (C.c_int, [C.c_char_p, C.c_long, C.c_long, C.c_long, C.POINTER(Cfg)]),
     "b200_workspace_bytes": (C.c_size_t, [C.c_char_p, C.POINTER(Cfg), C.c_long, C.c_long, C.c_long]),
     "b200_matmul_lhsT_rhs": (

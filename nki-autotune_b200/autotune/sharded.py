@@ -98,6 +98,86 @@ def cyclic_rows(M: int, rank: int, world: int, chunks: int) -> list[tuple[int, i
     return [((i * world + rank) * piece, (i * world + rank + 1) * piece) for i in range(chunks)]
 
 
+class PeerCopies:
+    """Every rank's copy of one ``[M, N]`` array, each mapped into every other rank's process.
+
+    ``local`` is this rank's copy (ordinary device memory of this GPU); the other ranks' copies are
+    mapped through CUDA IPC: every rank exports the allocation behind its copy, the 64-byte handles
+    travel with ``all_gather_object``, and every rank opens them with ITS OWN GPU current -- the
+    mapping is then valid for kernels of this GPU, and peer access to the owner is switched on.
+    ``push_rows`` stores a row range of the local copy into the same rows of every peer's copy with
+    the library's own kernel -- plain stores over NVLink, local reads only, no collective -- and
+    ``barrier`` is the stream-ordered meeting point after which every copy holds what every rank
+    pushed.  A rank may not push into rows that a peer is still reading: meet at ``barrier()``
+    first (or alternate two buffers).  ``close()`` unmaps; the owner's memory must outlive that.
+    """
+
+    def __init__(self, M: int, N: int, dtype=torch.bfloat16, device=None, group=None):
+        import ctypes as C
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.local = torch.empty((M, N), dtype=dtype, device=device)
+        self.row_bytes = N * self.local.element_size()
+        # (device, handle, size, offset of the storage inside the exported allocation, ...)
+        shared = self.local.untyped_storage()._share_cuda_()
+        mine = (bytes(shared[1]), int(shared[3]) + self.local.storage_offset() * self.local.element_size(), M * self.row_bytes)
+        table: list = [None] * self.world
+        dist.all_gather_object(table, mine, group=group)
+        self._bases: dict[int, int] = {}
+        self._ptrs: dict[int, int] = {}
+        lib = native.load()
+        with torch.cuda.device(device):
+            for r, (handle, offset, nbytes) in enumerate(table):
+                if r == self.rank:
+                    continue
+                if nbytes != M * self.row_bytes:
+                    raise RuntimeError(f"rank {self.rank}: rank {r} exported {nbytes} bytes, expected {M * self.row_bytes}")
+                # torch prefixes the 64-byte CUDA handle with a version and a kind byte ('c' = a plain
+                # cudaMalloc block; expandable segments are exported differently and are not handled)
+                if len(handle) not in (64, 65, 66) or (len(handle) > 64 and handle[-65:-64] != b"c"):
+                    raise RuntimeError(f"rank {self.rank}: rank {r} exported a handle of {len(handle)} bytes, kind {handle[:-64]!r}")
+                handle = handle[-64:]
+                base = C.c_void_p()
+                native.check(lib.b200_ipc_open(handle, C.byref(base)))
+                self._bases[r] = base.value
+                self._ptrs[r] = base.value + offset
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        self.barrier()
+
+    def push_rows(self, r0: int, r1: int, max_ctas: int = 0) -> None:
+        """Rows ``[r0, r1)`` of the local copy -> the same rows of every peer's copy (current stream)."""
+        import ctypes as C
+
+        if r1 <= r0 or not self._ptrs:
+            return
+        if r0 < 0 or r1 > self.local.shape[0]:
+            raise ValueError(f"rows [{r0}, {r1}) are outside the array of {self.local.shape[0]} rows")
+        ptrs = (C.c_void_p * len(self._ptrs))(*[p + r0 * self.row_bytes for _, p in sorted(self._ptrs.items())])
+        native.check(native.load().b200_peer_store(
+            self.local.data_ptr() + r0 * self.row_bytes, ptrs, len(self._ptrs), (r1 - r0) * self.row_bytes, int(max_ctas),
+            torch.cuda.current_stream(self.local.device).cuda_stream))
+
+    def barrier(self) -> None:
+        """Stream-ordered: past this point on the current stream, every rank's earlier pushes are in."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self) -> None:
+        """Unmap the peers' copies (after a barrier: nobody may still be pushing)."""
+        if self._bases:
+            self.barrier()
+            torch.cuda.synchronize(self.local.device)
+            lib = native.load()
+            with torch.cuda.device(self.local.device):
+                for base in self._bases.values():
+                    lib.b200_ipc_close(base)
+            self._bases, self._ptrs = {}, {}
+            self.barrier()
+            torch.cuda.synchronize(self.local.device)
+
+
 def matmul_lhsT_rhs_row_split(
     lhs_T_block: torch.Tensor,
     rhs: torch.Tensor,
@@ -109,6 +189,7 @@ def matmul_lhsT_rhs_row_split(
     matmul: Callable | None = None,
     chunks: int = 1,
     spare_ctas: int = 16,
+    peers: "PeerCopies | None" = None,
 ) -> tuple[torch.Tensor, torch.Tensor | None]:
     """This rank's rows of ``lhs_T.T @ rhs`` and, with ``gather``, the whole of C on every rank.
 
@@ -123,12 +204,46 @@ def matmul_lhsT_rhs_row_split(
     ``spare_ctas`` CTAs below the machine, which leaves the collective's CTAs room to be resident
     beside it.  Returns ``(None, out_full)`` in this mode: the rank's rows are not one block.
 
+    ``peers`` (a ``PeerCopies`` of shape ``[M, N]``; needs ``gather``): C is ``peers.local`` and the
+    exchange is this library's own peer-store kernel instead of the collective: each band's rows go
+    straight into every other GPU's copy of C over NVLink while the next band is multiplied, and one
+    small barrier at the end replaces the all-gathers.  Returns ``(None, peers.local)``.
+
     ``matmul(lhs_T_block, rhs, cfg=..., out=...)`` defaults to the tcgen05 GEMM.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     run = matmul if matmul is not None else kernels.matmul_lhsT_rhs
     n = rhs.shape[1]
+    if peers is not None:
+        if not gather or tuple(peers.local.shape) != (M, n):
+            raise ValueError(f"peers must hold [{M}, {n}] and needs gather=True")
+        out_full = peers.local
+        spans = [row_range(M, rank, world)] if chunks == 1 else cyclic_rows(M, rank, world, chunks)
+        if lhs_T_block.shape[1] != sum(b - a for a, b in spans):
+            raise ValueError(f"rank {rank}: lhs_T block has {lhs_T_block.shape[1]} columns, the split gives {sum(b - a for a, b in spans)}")
+        use_cfg = cfg
+        if matmul is None and spare_ctas > 0 and chunks > 1:
+            sms = torch.cuda.get_device_properties(lhs_T_block.device).multi_processor_count
+            base = dict(cfg) if cfg is not None else native.default_cfg("matmul_lhsT_rhs", spans[0][1] - spans[0][0], n, lhs_T_block.shape[0])
+            use_cfg = dict(base, _max_ctas=max(2, sms - spare_ctas))
+        comm = _comm_stream(lhs_T_block.device)
+        main = torch.cuda.current_stream(lhs_T_block.device)
+        comm.wait_stream(main)
+        col = 0
+        for p0, p1 in spans:
+            run(lhs_T_block[:, col:col + (p1 - p0)], rhs, cfg=use_cfg, out=out_full[p0:p1])
+            col += p1 - p0
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                # beside a GEMM the store kernel's CTAs crowd onto the SMs the GEMM leaves free: eight
+                # 256-thread CTAs per free SM keep enough stores in flight to fill the links
+                peers.push_rows(p0, p1, max_ctas=8 * spare_ctas if chunks > 1 else 0)
+        main.wait_stream(comm)
+        peers.barrier()
+        return None, out_full
     if chunks > 1:
         if not gather:
             raise ValueError("chunks > 1 is the overlapped all-gather: it needs gather=True")

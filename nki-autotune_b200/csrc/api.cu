@@ -1080,6 +1080,102 @@ extern "C" int b200_rmsnorm_matmul_noalloc(const void* x, const void* gamma, con
   return launch(pr, stream);
 }
 
+// ------------------------------------------------------------------- peer stores
+// The exchange step of the large-M row split without a collective library: every GPU pushes the
+// rows of C it has just computed into the same rows of every other GPU's copy of C, with plain
+// 16-byte stores through peer-mapped pointers (NVLink; every peer at full rate through the switch).
+// The kernel reads local memory only, waits for nothing and synchronises with nobody: the stores
+// are complete when the kernel is, and a stream-ordered barrier among the ranks afterwards makes
+// every copy of C whole.
+constexpr int PEER_MAX = 8;
+struct PeerDst {
+  uint4* p[PEER_MAX];
+  int n;
+};
+__global__ void __launch_bounds__(256) peer_store_kernel(const uint4* __restrict__ src, const PeerDst dst, const size_t n16) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // four independent 16-byte loads in flight per thread, each stored to every peer
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcs(src + i + u * stride);
+    for (int r = 0; r < dst.n; ++r) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) dst.p[r][i + u * stride] = v[u];
+    }
+  }
+  for (; i < n16; i += stride) {
+    const uint4 v = __ldcs(src + i);
+    for (int r = 0; r < dst.n; ++r) dst.p[r][i] = v;
+  }
+}
+
+extern "C" int b200_peer_store(const void* src, void* const* peer_dst, int n_peers, size_t bytes, int max_ctas, void* stream) {
+  if (n_peers == 0 || bytes == 0) return B200_OK;
+  if (!src || !peer_dst || n_peers < 0 || n_peers > PEER_MAX)
+    return set_error(B200_ERR_BAD_ARG, "peer_store: need a source, a pointer table and 1..%d peers (got %d)", PEER_MAX, n_peers);
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0 || bytes % 16 != 0)
+    return set_error(B200_ERR_BAD_ARG, "peer_store: source and byte count must be multiples of 16");
+  PeerDst d;
+  memset(&d, 0, sizeof(d));
+  d.n = n_peers;
+  for (int r = 0; r < n_peers; ++r) {
+    if (!peer_dst[r] || (reinterpret_cast<uintptr_t>(peer_dst[r]) & 15u) != 0)
+      return set_error(B200_ERR_BAD_ARG, "peer_store: destination %d is NULL or not 16-byte aligned", r);
+    d.p[r] = static_cast<uint4*>(peer_dst[r]);
+  }
+  // every destination must be device memory of another GPU that this GPU can reach, and peer
+  // access from this GPU to that one must be on in this process (mapping a peer's memory, e.g.
+  // through an IPC handle opened under the owner's device, does not turn it on by itself)
+  int cur = 0;
+  int rc = check_cuda(cudaGetDevice(&cur), "cudaGetDevice");
+  if (rc) return rc;
+  for (int r = 0; r < n_peers; ++r) {
+    cudaPointerAttributes at;
+    rc = check_cuda(cudaPointerGetAttributes(&at, peer_dst[r]), "peer_store: cudaPointerGetAttributes");
+    if (rc) return rc;
+    if (at.type != cudaMemoryTypeDevice)
+      return set_error(B200_ERR_BAD_ARG, "peer_store: destination %d is not device memory", r);
+    if (at.device == cur) continue;  // a local destination is fine too
+    int can = 0;
+    rc = check_cuda(cudaDeviceCanAccessPeer(&can, cur, at.device), "cudaDeviceCanAccessPeer");
+    if (rc) return rc;
+    if (!can) return set_error(B200_ERR_UNSUPPORTED, "peer_store: GPU %d cannot reach GPU %d", cur, at.device);
+    const cudaError_t e = cudaDeviceEnablePeerAccess(at.device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+    else if (e != cudaSuccess) return check_cuda(e, "cudaDeviceEnablePeerAccess");
+  }
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc) return rc;
+  const size_t n16 = bytes / 16;
+  long ctas = static_cast<long>(di.sm_count) * 4;
+  if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
+  const long need = static_cast<long>((n16 + 255) / 256);
+  if (ctas > need) ctas = need;
+  if (ctas < 1) ctas = 1;
+  peer_store_kernel<<<static_cast<unsigned>(ctas), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src), d, n16);
+  return check_cuda(cudaGetLastError(), "peer store launch");
+}
+
+// Maps an allocation that another process of this node exported with cudaIpcGetMemHandle into the
+// CURRENT device's address space, turning on peer access from the current device to the owner's
+// if they differ.  (A mapping made while the owner's device is current is of no use to kernels
+// of this GPU: the address is then valid on the owner's device only.)
+extern "C" int b200_ipc_open(const void* handle64, void** base) {
+  if (!handle64 || !base) return set_error(B200_ERR_BAD_ARG, "ipc_open: NULL pointer");
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof(h) == 64, "CUDA IPC memory handles are 64 bytes");
+  memcpy(&h, handle64, sizeof(h));
+  *base = nullptr;
+  return check_cuda(cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+}
+extern "C" int b200_ipc_close(void* base) {
+  if (!base) return B200_OK;
+  return check_cuda(cudaIpcCloseMemHandle(base), "cudaIpcCloseMemHandle");
+}
+
 // ------------------------------------------------------------------- checked build
 #ifdef B200_CHECKED_BUILD
 // Hands the wrappers arguments their checks must refuse.  Every access below is skipped by its

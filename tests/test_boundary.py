@@ -348,3 +348,23 @@ def test_guard_bands_notice_a_stray_write():
     backing[B.GUARD_BYTES + 5 * 7 * 2] = B.GUARD_PATTERN
     backing[B.GUARD_BYTES - 1] = 0                   # last byte before it
     assert not B.guards_intact(backing)
+
+
+def test_peer_store_refuses_bad_arguments_before_touching_a_device(native_lib):
+    """Argument checks of the exchange kernel's entry point need no GPU: nothing to do is fine, a
+    missing table, too many peers or a misaligned source or size is a bad argument."""
+    import ctypes as C
+
+    from autotune import native
+
+    table = (C.c_void_p * 9)(*[0x1000 * (i + 1) for i in range(9)])
+    assert native_lib.b200_peer_store(None, None, 0, 0, 0, None) == native.OK
+    assert native_lib.b200_peer_store(0x1000, table, 0, 4096, 0, None) == native.OK
+    assert native_lib.b200_peer_store(0x1000, None, 2, 4096, 0, None) == native.ERR_BAD_ARG
+    assert native_lib.b200_peer_store(0x1000, table, 9, 4096, 0, None) == native.ERR_BAD_ARG
+    assert native_lib.b200_peer_store(0x1008, table, 2, 4096, 0, None) == native.ERR_BAD_ARG
+    assert native_lib.b200_peer_store(0x1000, table, 2, 4100, 0, None) == native.ERR_BAD_ARG
+    assert "16" in native.last_error()
+    base = C.c_void_p()
+    assert native_lib.b200_ipc_open(None, C.byref(base)) == native.ERR_BAD_ARG
+    assert native_lib.b200_ipc_close(None) == native.OK

@@ -1,5 +1,6 @@
-"""Large-M row split over two GPUs: NCCL replication of rhs, local tcgen05 GEMMs, device all-gather;
-every rank compares its own block and its gathered copy of C with the CPU oracle.
+"""Large-M row split over two GPUs: NCCL replication of rhs, local tcgen05 GEMMs, device all-gather
+(and the library's own peer-store exchange); every rank compares its own block and its gathered
+copy of C with the CPU oracle.
 
 Needs two GPUs; skipped on a one-GPU box.  The ranks run as child processes under torchrun."""
 
@@ -44,6 +45,24 @@ SCRIPT = textwrap.dedent(
         err = O.max_abs_rel_err(kernels.to_host(full).astype(np.float32), want)
         err_block = O.max_abs_rel_err(kernels.to_host(block).astype(np.float32), want[m0:m1])
         res[str(M)] = [bool(torch.equal(rhs, rhs_src)), max(err, err_block), list(full.shape)]
+        if M % (8 * world * 4) == 0:
+            # the same products with the library's own exchange: rows pushed into every peer's copy of
+            # C over NVLink (CUDA IPC mappings, plain stores), one block per rank and block-cyclic
+            from autotune.sharded import PeerCopies, cyclic_rows
+            peers = PeerCopies(M, N)
+            errs = []
+            for chunks in (1, 4):
+                peers.local.zero_()
+                torch.cuda.synchronize(); dist.barrier()
+                spans = [row_range(M, rank, world)] if chunks == 1 else cyclic_rows(M, rank, world, chunks)
+                cols = torch.cat([lhs_T[:, a:b] for a, b in spans], dim=1).contiguous()
+                for _ in range(2):   # twice: the second run overwrites what the first pushed
+                    _, c_all = matmul_lhsT_rhs_row_split(cols, rhs, M, chunks=chunks, peers=peers)
+                torch.cuda.synchronize()
+                errs.append(O.max_abs_rel_err(kernels.to_host(c_all).astype(np.float32), want))
+                dist.barrier()
+            res["peers"] = errs
+            peers.close()
     out = [None] * world
     dist.all_gather_object(out, res)
     if rank == 0:
@@ -70,3 +89,4 @@ def test_row_split_two_gpus_nccl(native_lib, tmp_path):
         for key, shape in (("4096", [4096, 384]), ("1000", [1000, 136])):
             same_rhs, err, got_shape = r[key]
             assert same_rhs and err <= 1e-2 and got_shape == shape
+        assert len(r["peers"]) == 2 and max(r["peers"]) <= 1e-2, r["peers"]
