@@ -742,24 +742,30 @@ def run_extras(ranks: Ranks, torch, kernels, args, vendor_args=None) -> dict:
         # the same block-cyclic split with the library's own exchange: every band's rows are pushed
         # into the other GPUs' copies of C by a kernel of plain peer stores while the next band is
         # multiplied; no collective but one small barrier at the end
-        peers = sharded.PeerCopies(Mt, Nx, group=grp)
-        full_local = full
-        full = peers.local  # (check() reads `full`)
-        full.zero_()
-        step_ps = lambda: sharded.matmul_lhsT_rhs_row_split(a, rep, Mt, cfg=cfg, group=grp, chunks=chunks, peers=peers)
-        for _ in range(2):
-            step_ps()
-        ms_ps = timed_region(ranks, torch, step_ps, 5)
-        errs_ps = ranks.gather(check(lambda r, j: ((j // piece) * ranks.world + r) * piece + j % piece))
-        peers.close()
-        full = full_local
+        ms_ps, errs_ps, ps_problem = None, None, None
+        try:
+            peers = sharded.PeerCopies(Mt, Nx, group=grp)  # (raises on every rank or on none)
+        except RuntimeError as exc:
+            peers, ps_problem = None, str(exc)[:300]
+        if peers is not None:
+            full_local = full
+            full = peers.local  # (check() reads `full`)
+            full.zero_()
+            step_ps = lambda: sharded.matmul_lhsT_rhs_row_split(a, rep, Mt, cfg=cfg, group=grp, chunks=chunks, peers=peers)
+            for _ in range(2):
+                step_ps()
+            ms_ps = timed_region(ranks, torch, step_ps, 5)
+            errs_ps = ranks.gather(check(lambda r, j: ((j // piece) * ranks.world + r) * piece + j % piece))
+            peers.close()
+            full = full_local
         if ranks.rank == 0:
             gather_bytes = int(Mt * Nx * 2 * (ranks.world - 1) / ranks.world)
             row.update({
                 "rhs_broadcast_ms": round(ms_rep, 4), "with_device_allgather_ms": round(ms_all, 4),
                 "with_overlapped_allgather_ms": round(ms_ov, 4),
-                "with_peer_stores_ms": round(ms_ps, 4),
-                "aggregate_tflops_with_allgather": round(2.0 * Mt * Nx * Kx / min(ms_all, ms_ov, ms_ps) / 1e9, 1),
+                "with_peer_stores_ms": round(ms_ps, 4) if ms_ps is not None else None,
+                "peer_stores_unavailable": ps_problem,
+                "aggregate_tflops_with_allgather": round(2.0 * Mt * Nx * Kx / min(x for x in (ms_all, ms_ov, ms_ps) if x is not None) / 1e9, 1),
                 "allgather_bytes_per_gpu": gather_bytes,
                 "allgather_alone_bound_ms_at_770_gbs": round(gather_bytes / 770e9 * 1e3, 4),
                 "overlap": f"block-cyclic split, {chunks} bands, GEMM grid 16 CTAs below the machine, all-gather of band i-1 beside the GEMM of band i",
@@ -768,9 +774,9 @@ def run_extras(ranks: Ranks, torch, kernels, args, vendor_args=None) -> dict:
                     "rows_checked_per_rank": 4 * ranks.world, "tol": 1e-2,
                     "max_abs_rel_err_per_rank": [float(f"{e:.3e}") for e in errs],
                     "max_abs_rel_err_per_rank_overlapped": [float(f"{e:.3e}") for e in errs_ov],
-                    "max_abs_rel_err_per_rank_peer_stores": [float(f"{e:.3e}") for e in errs_ps]},
+                    "max_abs_rel_err_per_rank_peer_stores": [float(f"{e:.3e}") for e in errs_ps] if errs_ps else None},
             })
-        del rep, full, full_local, peers
+        del rep, full, peers
     if ranks.rank == 0:
         extras["large_m_row_split_131072x4096x4096"] = row
     del a, b

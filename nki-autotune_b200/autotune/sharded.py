@@ -129,21 +129,34 @@ class PeerCopies:
         self._bases: dict[int, int] = {}
         self._ptrs: dict[int, int] = {}
         lib = native.load()
-        with torch.cuda.device(device):
-            for r, (handle, offset, nbytes) in enumerate(table):
-                if r == self.rank:
-                    continue
-                if nbytes != M * self.row_bytes:
-                    raise RuntimeError(f"rank {self.rank}: rank {r} exported {nbytes} bytes, expected {M * self.row_bytes}")
-                # torch prefixes the 64-byte CUDA handle with a version and a kind byte ('c' = a plain
-                # cudaMalloc block; expandable segments are exported differently and are not handled)
-                if len(handle) not in (64, 65, 66) or (len(handle) > 64 and handle[-65:-64] != b"c"):
-                    raise RuntimeError(f"rank {self.rank}: rank {r} exported a handle of {len(handle)} bytes, kind {handle[:-64]!r}")
-                handle = handle[-64:]
-                base = C.c_void_p()
-                native.check(lib.b200_ipc_open(handle, C.byref(base)))
-                self._bases[r] = base.value
-                self._ptrs[r] = base.value + offset
+        problem = None
+        try:
+            with torch.cuda.device(device):
+                for r, (handle, offset, nbytes) in enumerate(table):
+                    if r == self.rank:
+                        continue
+                    if nbytes != M * self.row_bytes:
+                        raise RuntimeError(f"rank {r} exported {nbytes} bytes, expected {M * self.row_bytes}")
+                    # torch prefixes the 64-byte CUDA handle with a version and a kind byte ('c' = a plain
+                    # cudaMalloc block; expandable segments are exported differently and are not handled)
+                    if len(handle) not in (64, 65, 66) or (len(handle) > 64 and handle[-65:-64] != b"c"):
+                        raise RuntimeError(f"rank {r} exported a handle of {len(handle)} bytes, kind {handle[:-64]!r}")
+                    base = C.c_void_p()
+                    native.check(lib.b200_ipc_open(handle[-64:], C.byref(base)))
+                    self._bases[r] = base.value
+                    self._ptrs[r] = base.value + offset
+        except Exception as exc:  # noqa: BLE001 - reported to every rank below
+            problem = f"rank {self.rank}: {exc}"
+        # every rank learns whether every rank could map every copy: either all go on or all raise
+        # (a rank that raised alone would leave the others waiting in the first barrier)
+        problems: list = [None] * self.world
+        dist.all_gather_object(problems, problem, group=group)
+        if any(problems):
+            with torch.cuda.device(device):
+                for base in self._bases.values():
+                    lib.b200_ipc_close(base)
+            self._bases, self._ptrs = {}, {}
+            raise RuntimeError("peer mappings could not be made: " + "; ".join(p for p in problems if p))
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         self.barrier()
 
