@@ -34,7 +34,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=131072)
     ap.add_argument("--overlap", action="store_true")
-    ap.add_argument("--chunks", type=int, default=8)
+    ap.add_argument("--chunks", type=int, default=0, help="bands of the block-cyclic split (default: 8 with --overlap, 4 with --peer-stores)")
     ap.add_argument("--peer-stores", action="store_true")
     args = ap.parse_args()
 
@@ -48,7 +48,7 @@ def main() -> None:
     # every rank draws the same seeded tensors (the recipe of the benchmark configuration) and keeps its share
     t = generate_tensors({"lhs_T": {"shape": [K, M], "dtype": "bfloat16", "dist": d},
                           "rhs": {"shape": [K, N], "dtype": "bfloat16", "dist": d}}, seed=4)
-    chunks = args.chunks if (args.overlap or args.peer_stores) else 1
+    chunks = (args.chunks or (4 if args.peer_stores else 8)) if (args.overlap or args.peer_stores) else 1
     if chunks > 1:
         pieces = sharded.cyclic_rows(M, rank, world, chunks)
     else:
