@@ -231,6 +231,8 @@ def matmul_lhsT_rhs_row_split(
     if peers is not None:
         if not gather or tuple(peers.local.shape) != (M, n):
             raise ValueError(f"peers must hold [{M}, {n}] and needs gather=True")
+        if not lhs_T_block.is_cuda or peers.local.device != lhs_T_block.device:
+            raise ValueError("the peer-store exchange runs on the GPU that holds this rank's copy of C")
         out_full = peers.local
         spans = [row_range(M, rank, world)] if chunks == 1 else cyclic_rows(M, rank, world, chunks)
         if lhs_T_block.shape[1] != sum(b - a for a, b in spans):
