@@ -10,7 +10,7 @@ block-cyclic split, where the all-gather of one band runs beside the GEMM of the
 ``--peer-stores``: the same split with the library's own exchange, a kernel that stores each band's
 rows into the other GPUs' copies of C over NVLink, in place of the collective).  Rank 0
 then gathers nothing more: every rank checks rows of ITS copy of C against a host product of the same
-inputs (fp32 BLAS on the bf16-rounded values) and the ranks' verdicts are
+inputs (fp32 BLAS on the bf16-rounded values) and the ranks' results are
 collected on the host.  The reference has no multi-device path (its benchmark loop is one device:
 ``autotune/src/autotune/runner/driver.py:97``).
 """
