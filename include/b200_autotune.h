@@ -39,7 +39,7 @@ typedef enum b200_status {
 
 /* Meta-parameters of one autotune candidate.  These are what the sweep enumerates in
  * place of the reference's schedule transforms (tensorize Split factors, multi-buffer
- * counts, SoftwarePipeline stages, Reorder; nkigym/src/nkigym/transforms/*.py) and of
+ * counts, SoftwarePipeline stages, Reorder; the modules under nkigym/src/nkigym/transforms/) and of
  * KernelJob.lnc (autotune/src/autotune/runner/types.py:50). */
 typedef struct b200_cfg {
   int tile_m;     /* output-tile rows per CTA group: 128 or 256; 512 with cluster_m 2 (plain GEMM

@@ -368,3 +368,31 @@ def test_peer_store_refuses_bad_arguments_before_touching_a_device(native_lib):
     base = C.c_void_p()
     assert native_lib.b200_ipc_open(None, C.byref(base)) == native.ERR_BAD_ARG
     assert native_lib.b200_ipc_close(None) == native.OK
+
+
+def test_header_is_plain_c_and_links_against_the_library(native_lib, tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 with warnings as errors, and a C program
+    that calls into the library links and runs (no compute: version, a budget check, an error text)."""
+    import shutil
+    import subprocess
+
+    from autotune import native
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "use_header.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <string.h>\n#include "b200_autotune.h"\n'
+        "int main(void) {\n"
+        "  b200_cfg c; long smem = 0; int tmem = 0; memset(&c, 0, sizeof c);\n"
+        "  c.tile_m = 128; c.tile_n = 256; c.tile_k = 64; c.stages = 5; c.cluster_m = 1; c.cluster_n = 1;\n"
+        '  int rc = b200_cfg_check("matmul_lhsT_rhs", &c, 8192, 8192, 8192, &smem, &tmem);\n'
+        '  printf("%d %d %ld %d %s\\n", b200_abi_version(), rc, smem, tmem, b200_last_error());\n'
+        "  return 0;\n}\n")
+    exe = tmp_path / "use_header"
+    lib_dir = str(native.LIB_PATH.parent)
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", str(REPO / "include"), str(src),
+                    "-L", lib_dir, "-lb200_autotune", f"-Wl,-rpath,{lib_dir}", "-o", str(exe)], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split(None, 4)
+    assert out[0] == "1" and int(out[1]) == native.ERR_SMEM_OOM and int(out[2]) > 232448 and "Out of memory in smem" in out[4]
