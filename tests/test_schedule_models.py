@@ -1,4 +1,4 @@
-"""CPU models of two pieces of device-side bookkeeping, checked against what the planner emits.
+"""CPU models of three pieces of device-side bookkeeping, checked against what the planner emits.
 
 1. The mbarrier ring protocol of the inline fused kernel (TMA producer of x tiles -> transform warp
    groups taking k-blocks round-robin -> UMMA issuer, over a shared-memory ring and a tensor-memory
@@ -8,6 +8,9 @@
    agrees with what the waiter means.  It must pass for every ring the planner can emit and fail
    for ring depths that are not a multiple of the group count (the one GPU fault on record came
    from exactly that).
+
+1b. The hand-over of a single-buffered accumulator in halves between the UMMA issuer and the
+   epilogue warps of the plain GEMM (commits that arrive late and in order, 8 or 16 warps).
 
 2. The tile split of the weight-streaming kernel (whole tiles, owners, donors): every
    (tile, k-block) is streamed exactly once, donors' slots are unique, and the contributor range
@@ -148,6 +151,118 @@ def test_ring_depths_that_are_not_multiples_of_the_group_count_are_caught(a_stag
 def test_plain_single_consumer_rings_pass():
     for depth in (1, 2, 3, 4, 6, 12):
         check_ring(depth, depth, 1)
+
+
+# ------------------------------------------------------------------------------------------------
+# 1b. accumulator handed over in halves (plain GEMM, single accumulator of two UMMA blocks)
+# ------------------------------------------------------------------------------------------------
+# acc_full[h] / acc_empty[h] stand for half h and flip once per tile.  The issuer issues half 0 and
+# half 1 one after the other in every k-block; the last k-block commits half 0 between them, the
+# first one waits for half 1 to be drained between them.  A commit arrives when the UMMAs before it
+# have completed: later than it is issued, in issue order.  Every epilogue warp drains half 0,
+# hands it back, then drains half 1.
+def halves_issuer(bars, tiles, nkb):
+    ph = 0
+    for t in range(tiles):
+        yield ("wait", bars["acc_empty"][0], ph ^ 1, t)
+        for kb in range(nkb):
+            if kb == nkb - 1:
+                yield ("commit", bars["acc_full"][0])          # after half 0's UMMAs of the last k-block
+            if kb == 0:
+                yield ("wait", bars["acc_empty"][1], ph ^ 1, t)
+        yield ("commit", bars["acc_full"][1])
+        ph ^= 1
+
+
+def halves_epilogue_warp(bars, tiles):
+    ph = 0
+    for t in range(tiles):
+        for h in (0, 1):
+            yield ("wait", bars["acc_full"][h], ph, t + 1)
+            yield ("arrive", bars["acc_empty"][h])
+        ph ^= 1
+
+
+def run_halves_model(tiles, nkb, warps, seed, bias=None):
+    rng = random.Random(seed)
+    bars = {"acc_full": [Barrier(1), Barrier(1)], "acc_empty": [Barrier(warps), Barrier(warps)]}
+    agents = [halves_issuer(bars, tiles, nkb)] + [halves_epilogue_warp(bars, tiles) for _ in range(warps)]
+    pending = [next(a, None) for a in agents]
+    commits = []   # issued, not yet arrived; they arrive in issue order
+    while any(op is not None for op in pending) or commits:
+        if commits and (rng.random() < 0.3 or all(op is None for op in pending)):
+            commits.pop(0).arrive()
+            continue
+        live = [i for i, op in enumerate(pending) if op is not None]
+        progressed = False
+        for i in sorted(live, key=lambda i: (bias(i) if bias else 0, rng.random())):
+            op = pending[i]
+            if op[0] == "arrive":
+                op[1].arrive()
+            elif op[0] == "commit":
+                commits.append(op[1])
+            else:
+                _, bar, parity, need = op
+                says, means = bar.parity_test(parity), bar.completed >= need
+                if says != means:
+                    raise Violation(f"agent {i}: parity test says {says}, {bar.completed} phases complete, {need} needed")
+                if not says:
+                    continue
+            pending[i] = next(agents[i], None)
+            progressed = True
+            break
+        if not progressed:
+            if not commits:
+                raise Violation("deadlock: every agent is blocked")
+            commits.pop(0).arrive()
+    assert all(b.completed == tiles for pair in bars.values() for b in pair)
+
+
+def test_accumulator_halves_protocol():
+    """One to several tiles, tiles of one, two and many k-blocks, 8 warps (one CTA) and 16 (a pair)."""
+    for tiles, nkb, warps in itertools.product((1, 2, 5), (1, 2, 7), (8, 16)):
+        for bias in BIASES:
+            for seed in range(3):
+                run_halves_model(tiles, nkb, warps, seed, bias)
+
+
+def test_halves_model_notices_a_missing_hand_back():
+    """An issuer that does not wait for half 1 to be drained before the next tile's first k-block
+    would be caught as a barrier that ends with the wrong number of completed phases -- here: the
+    model's own bookkeeping of an epilogue that forgets to hand half 1 back deadlocks."""
+    def forgetful(bars, tiles):
+        ph = 0
+        for t in range(tiles):
+            yield ("wait", bars["acc_full"][0], ph, t + 1)
+            yield ("arrive", bars["acc_empty"][0])
+            yield ("wait", bars["acc_full"][1], ph, t + 1)      # drains half 1 but never releases it
+            ph ^= 1
+
+    bars = {"acc_full": [Barrier(1), Barrier(1)], "acc_empty": [Barrier(1), Barrier(1)]}
+    agents = [halves_issuer(bars, 2, 3), forgetful(bars, 2)]
+    pending = [next(a, None) for a in agents]
+    commits, steps = [], 0
+    with pytest.raises(Violation):
+        while any(op is not None for op in pending) or commits:
+            steps += 1
+            progressed = False
+            if commits:
+                commits.pop(0).arrive()
+                progressed = True
+            for i, op in enumerate(pending):
+                if op is None:
+                    continue
+                if op[0] == "arrive":
+                    op[1].arrive()
+                elif op[0] == "commit":
+                    commits.append(op[1])
+                else:
+                    if not op[1].parity_test(op[2]):
+                        continue
+                pending[i] = next(agents[i], None)
+                progressed = True
+            if not progressed:
+                raise Violation("deadlock: every agent is blocked")
 
 
 # ------------------------------------------------------------------------------------------------
