@@ -98,6 +98,19 @@ def cyclic_rows(M: int, rank: int, world: int, chunks: int) -> list[tuple[int, i
     return [((i * world + rank) * piece, (i * world + rank + 1) * piece) for i in range(chunks)]
 
 
+def cuda_ipc_handle(exported: bytes) -> bytes:
+    """The 64-byte ``cudaIpcMemHandle_t`` inside what ``UntypedStorage._share_cuda_()`` returns.
+
+    torch prefixes the handle with a version byte and a kind byte (older versions: the kind byte
+    only, or nothing): kind ``c`` is a plain ``cudaMalloc`` block.  Memory of an expandable segment
+    (kind ``e``) is exported as file descriptors, not as a CUDA IPC handle, and is refused here.
+    """
+    exported = bytes(exported)
+    if len(exported) not in (64, 65, 66) or (len(exported) > 64 and exported[-65:-64] != b"c"):
+        raise RuntimeError(f"not a CUDA IPC handle of a cudaMalloc block: {len(exported)} bytes, prefix {exported[:-64]!r}")
+    return exported[-64:]
+
+
 class PeerCopies:
     """Every rank's copy of one ``[M, N]`` array, each mapped into every other rank's process.
 
@@ -137,12 +150,8 @@ class PeerCopies:
                         continue
                     if nbytes != M * self.row_bytes:
                         raise RuntimeError(f"rank {r} exported {nbytes} bytes, expected {M * self.row_bytes}")
-                    # torch prefixes the 64-byte CUDA handle with a version and a kind byte ('c' = a plain
-                    # cudaMalloc block; expandable segments are exported differently and are not handled)
-                    if len(handle) not in (64, 65, 66) or (len(handle) > 64 and handle[-65:-64] != b"c"):
-                        raise RuntimeError(f"rank {r} exported a handle of {len(handle)} bytes, kind {handle[:-64]!r}")
                     base = C.c_void_p()
-                    native.check(lib.b200_ipc_open(handle[-64:], C.byref(base)))
+                    native.check(lib.b200_ipc_open(cuda_ipc_handle(handle), C.byref(base)))
                     self._bases[r] = base.value
                     self._ptrs[r] = base.value + offset
         except Exception as exc:  # noqa: BLE001 - reported to every rank below

@@ -396,3 +396,15 @@ def test_header_is_plain_c_and_links_against_the_library(native_lib, tmp_path):
                     "-L", lib_dir, "-lb200_autotune", f"-Wl,-rpath,{lib_dir}", "-o", str(exe)], check=True, capture_output=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split(None, 4)
     assert out[0] == "1" and int(out[1]) == native.ERR_SMEM_OOM and int(out[2]) > 232448 and "Out of memory in smem" in out[4]
+
+
+def test_cuda_ipc_handle_is_taken_out_of_what_torch_exports():
+    from autotune.sharded import cuda_ipc_handle
+
+    raw = bytes(range(64))
+    assert cuda_ipc_handle(raw) == raw
+    assert cuda_ipc_handle(b"c" + raw) == raw
+    assert cuda_ipc_handle(b"\x01c" + raw) == raw
+    for bad in (b"\x01e" + raw, b"e" + raw, raw[:63], b"\x01\x01c" + raw):
+        with pytest.raises(RuntimeError, match="not a CUDA IPC handle"):
+            cuda_ipc_handle(bad)
