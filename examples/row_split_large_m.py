@@ -1,7 +1,7 @@
 """The large-M product split by rows of C over the GPUs of one box.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        examples/row_split_large_m.py [--m 131072] [--overlap] [--peer-stores]
+        examples/row_split_large_m.py [--rows 131072] [--overlap] [--peer-stores]
 
 C[M, 4096] = lhsT[4096, M]^T . rhs[4096, 4096] with M = 131072 (seed 4, N(0,1)/sqrt(K), bf16): rank r
 multiplies its share of the columns of lhsT by the whole of rhs.  rhs is uploaded by rank 0 only and
@@ -32,7 +32,8 @@ from autotune.runner.benchmark import generate_tensors  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=131072)
+    # (not "--m": the launcher's own parser takes that for an abbreviation of its options)
+    ap.add_argument("--rows", dest="m", type=int, default=131072, help="M, the rows of C")
     ap.add_argument("--overlap", action="store_true")
     ap.add_argument("--chunks", type=int, default=0, help="bands of the block-cyclic split (default: 8 with --overlap, 4 with --peer-stores)")
     ap.add_argument("--peer-stores", action="store_true")
