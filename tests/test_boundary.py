@@ -408,3 +408,32 @@ def test_cuda_ipc_handle_is_taken_out_of_what_torch_exports():
     for bad in (b"\x01e" + raw, b"e" + raw, raw[:63], b"\x01\x01c" + raw):
         with pytest.raises(RuntimeError, match="not a CUDA IPC handle"):
             cuda_ipc_handle(bad)
+
+
+def test_planner_answers_every_candidate_with_a_status_and_consistent_budgets(native_lib):
+    """Every point of a wide grid of meta-parameters, sensible or not, gets one of the declared status
+    codes; an accepted point fits the budgets it reports, and its launch description parses."""
+    import itertools
+
+    from autotune import native
+
+    known = {native.OK, native.ERR_BAD_SHAPE, native.ERR_UNSUPPORTED, native.ERR_SMEM_OOM, native.ERR_TMEM_OOM}
+    shapes = [(8192, 8192, 8192), (4096, 11008, 4096), (16, 28672, 8192), (136, 72, 64), (8, 8, 64)]
+    accepted = 0
+    for fam in ("matmul_lhsT_rhs", "matmul_lhs_rhs", "rmsnorm_matmul"):
+        for tm, tn, tk, st, cm, nm, sk in itertools.product((16, 64, 128, 256, 512), (32, 64, 128, 256, 512), (32, 64, 96, 128),
+                                                            (1, 3, 6, 13), (1, 2), (0, 1, 2), (0, 4)):
+            cfg = dict(tile_m=tm, tile_n=tn, tile_k=tk, stages=st, cluster_m=cm, norm_mode=nm, split_k=sk)
+            M, N, K = shapes[(tm + tn + tk + st + cm + nm + sk) % len(shapes)]
+            if fam == "rmsnorm_matmul" and M > 16 and nm == 0:
+                cfg["norm_mode"] = 2   # as compile_one resolves it: the sweep always supplies scratch
+            status, msg, smem, tmem = native.cfg_check(fam, cfg, M, N, K)
+            assert status in known, (fam, cfg, status, msg)
+            assert (status == native.OK) == (msg == "")
+            if status == native.OK:
+                accepted += 1
+                assert 0 < smem <= 232448 and tmem in (32, 64, 128, 256, 512), (fam, cfg, smem, tmem)
+                plan = native.describe_launch(fam, cfg, M, N, K)
+                assert 1 <= plan["grid"] <= 160 and plan["threads"] % 32 == 0 and plan["threads"] > 0
+                assert plan["smem_bytes"] <= 232448
+    assert accepted > 100
