@@ -88,6 +88,10 @@ int b200_device_count(int* count);
  * tensor-memory columns the candidate needs and returns B200_ERR_SMEM_OOM /
  * B200_ERR_TMEM_OOM / B200_ERR_UNSUPPORTED / B200_ERR_BAD_SHAPE when it cannot run.
  * family is "matmul_lhsT_rhs", "matmul_lhs_rhs" or "rmsnorm_matmul".
+ * (rmsnorm_matmul, M > 16, norm_mode 0: which variant runs is only decided at the call, by
+ * whether scratch is passed; this check then answers for the inline variant -- ask with
+ * norm_mode 2 for the variant that runs with scratch, which is what b200_describe_launch
+ * describes and what the sweep does.)
  * Stands in for the compile step, compile_one(), autotune/src/autotune/runner/compile.py:197-244:
  * an over-subscribed candidate is a reported failure, never silently dropped. */
 int b200_cfg_check(const char* family, const b200_cfg* cfg, long M, long N, long K,
